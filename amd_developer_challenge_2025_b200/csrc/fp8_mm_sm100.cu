@@ -1,0 +1,849 @@
+// FP8 (e4m3fn) block-scaled GEMM for NVIDIA B200 (sm_100a), bf16 output.
+//
+// Replaces the reference's HIP/MFMA kernels fp8_mm_128x128_ft2, fp8_mm_128x128_pt,
+// insitu_transpose_128x128, fp8_mm_128x128_ft2_split4(+_merge) and
+// fp8_mm_32x32_16x16_ft2 (1-amd-fp8-mm/amd-fp8-mm-submission.py:18-511) and the host
+// dispatcher fp8_mm (same file, 514-579). The arithmetic kept from the reference is its
+// K loop (same file, 302-357): per 128-wide K block the matrix unit accumulates
+// P = sum a*b in fp32 from zero, then acc += P * a_scale[row,kb] * b_scale[col/128,kb]
+// in fp32 on the vector ALU, and one fp32 -> bf16 rounding at the end.
+//
+// Structure of one CTA (384 threads, one CTA per SM, persistent over work items):
+//   warp 0      TMA producer: A (128 x 128 B) and B (BN x 128 B) tiles of one K block into a
+//               SWIZZLE_128B shared-memory ring, completion on an mbarrier per stage
+//   warp 1      MMA issuer: 4 x tcgen05.mma.kind::f8f6f4 (K=32 each) per K block into one of
+//               the TMEM partial buffers, tcgen05.commit to free the stage and publish the buffer
+//   warp 2      allocates / frees TMEM
+//   warps 4-11  promotion + store: tcgen05.ld the partial, fma into register accumulators with
+//               the per-row, per-block scale, then bf16 stores (or split-K partials + last-arriver
+//               reduction)
+// Every mbarrier wait is bounded: when it expires the kernel writes a status word and all roles
+// leave their loops; nothing traps and nothing spins without limit.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "b200_fp8_mm.h"
+
+namespace {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 128;  // bytes of e4m3 per row of a stage = one scale block = one 128B swizzle row
+constexpr int kUmmaK = 32;
+constexpr int kNumEpiWarps = 8;
+constexpr int kNumEpiThreads = kNumEpiWarps * 32;
+constexpr int kNumThreads = 128 + kNumEpiThreads;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr int kCounterBytes = 4096;
+constexpr int kMaxCounters = kCounterBytes / 4;
+
+struct KernelParams {
+  const float* a_scale;
+  const float* b_scale;
+  __nv_bfloat16* c;
+  float* partials;  // split-K planes, tile-blocked
+  int* counters;    // one per output tile, zero between launches
+  int* status;      // may be null
+  long long sa_m, sa_k, sb_n, sb_k, ldc;
+  int M, N, K;
+  int n_phase;
+  int tiles_m, tiles_n, split_k, kblocks;
+  int raster_group;
+  int b_scale_rows;
+  int vec_store;  // 1 when c, ldc and N allow 16-byte stores
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Shared flag every role polls while it waits; set by the first wait that expires.
+struct AbortCtx {
+  volatile int* abort_flag;  // shared memory
+  int* status;               // global, may be null
+};
+
+// Bounded wait. Returns false when the wait expired here or in another role.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where) {
+  const unsigned long long t0 = global_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0xffu) == 0) {
+      if (*ctx.abort_flag) return false;
+      if (global_ns() - t0 > kWaitLimitNs) {
+        *ctx.abort_flag = 1;
+        if (ctx.status != nullptr) {
+          if (atomicCAS(ctx.status, 0, B200_FP8_MM_DEV_WAIT_EXPIRED) == 0) {
+            ctx.status[1] = where;
+            ctx.status[2] = static_cast<int>(blockIdx.x);
+            ctx.status[3] = static_cast<int>(parity);
+          }
+        }
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, ctx, where);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+// 32 lanes x 32 columns of fp32: thread t of the warp receives lane (base lane + t).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Waits for this thread's outstanding tcgen05.ld; the registers pass through the statement so
+// that no use of them can be scheduled above it.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+        "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+        "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+        "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+      :
+      : "memory");
+}
+
+__device__ __forceinline__ void epi_bar_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiThreads) : "memory");
+}
+
+// acc.xy += p.xy * s.xy with one packed instruction.
+__device__ __forceinline__ void fma2(float2& acc, uint32_t p0, uint32_t p1, const float2& s) {
+  asm("{\n\t.reg .b64 pp, ss, aa;\n\t"
+      "mov.b64 pp, {%2, %3};\n\t"
+      "mov.b64 ss, {%4, %5};\n\t"
+      "mov.b64 aa, {%0, %1};\n\t"
+      "fma.rn.f32x2 aa, pp, ss, aa;\n\t"
+      "mov.b64 {%0, %1}, aa;\n\t}"
+      : "+f"(acc.x), "+f"(acc.y)
+      : "r"(p0), "r"(p1), "f"(s.x), "f"(s.y));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// K-major, SWIZZLE_128B shared-memory matrix descriptor (sm_100 format): start address and
+// stride-dimension offset in 16-byte units, 8-row groups 1024 bytes apart, version 1, layout 2.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// kind::f8f6f4 instruction descriptor: D = fp32, A = B = e4m3, both K-major, M = 128, N = block_n.
+__host__ __device__ constexpr uint32_t make_idesc(int block_n) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) |
+         (static_cast<uint32_t>(block_n >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+}
+
+template <int BN>
+struct TileCfg {
+  static constexpr int kStageBytesA = kBlockM * kBlockK;
+  static constexpr int kStageBytesB = BN * kBlockK;
+  static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
+  static constexpr int kTmemBufs = (BN <= 128) ? 4 : 2;
+  static constexpr int kTmemColsUsed = kTmemBufs * BN;
+  static constexpr int kTmemCols = kTmemColsUsed <= 256 ? 256 : 512;  // power of two >= 32
+  static constexpr int kColsPerThread = BN / 2;                        // two epilogue warpgroups
+  static constexpr int kChunks = kColsPerThread / 32;
+  static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "block_n must be 64, 128, 192 or 256");
+};
+
+struct WorkItem {
+  int m0, n0, tile, split, kb_begin, kb_end;
+};
+
+__device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, int block_n) {
+  WorkItem it;
+  it.split = w % p.split_k;
+  const int t = w / p.split_k;
+  it.tile = t;
+  const int per_group = p.raster_group * p.tiles_n;
+  const int group = t / per_group;
+  const int first_m = group * p.raster_group;
+  const int gsize = min(p.raster_group, p.tiles_m - first_m);
+  const int within = t - group * per_group;
+  const int tm = first_m + within % gsize;
+  const int tn = within / gsize;
+  it.m0 = tm * kBlockM;
+  it.n0 = tn * block_n;
+  it.kb_begin = static_cast<int>((static_cast<long long>(it.split) * p.kblocks) / p.split_k);
+  it.kb_end = static_cast<int>((static_cast<long long>(it.split + 1) * p.kblocks) / p.split_k);
+  return it;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kNumThreads, 1)
+fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const KernelParams p) {
+  using Cfg = TileCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // SWIZZLE_128B tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + Cfg::kTmemBufs;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * Cfg::kTmemBufs);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
+
+  const int warp = static_cast<int>(threadIdx.x) >> 5;
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const AbortCtx ctx{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < Cfg::kTmemBufs; ++b) {
+      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), kNumEpiWarps);
+    }
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)),
+                 "r"(Cfg::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  const int total_work = p.tiles_m * p.tiles_n * p.split_k;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const WorkItem it = decode_work(p, w, BN);
+        for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, ctx, 0x100 | stage)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = smem_u32(&full_bar[stage]);
+          mbar_expect_tx(fb, Cfg::kStageBytes);
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          tma_load_2d(sa, &tmap_a, kb * kBlockK, it.m0, fb);
+          tma_load_2d(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, it.n0, fb);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      int stage = 0, buf = 0;
+      uint32_t phase = 0, bphase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const WorkItem it = decode_work(p, w, BN);
+        for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+          if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), bphase ^ 1u, ctx, 0x200 | buf) ||
+              !mbar_wait(smem_u32(&full_bar[stage]), phase, ctx, 0x300 | stage)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint64_t desc_a = make_smem_desc(sa);
+          const uint64_t desc_b = make_smem_desc(sa + Cfg::kStageBytesA);
+          const uint32_t d_addr = tmem_base + static_cast<uint32_t>(buf * BN);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // 32 bytes further along K inside the 128-byte swizzle row = +2 in 16-byte units.
+            umma_f8(d_addr, desc_a + static_cast<uint64_t>(2 * k), desc_b + static_cast<uint64_t>(2 * k), idesc,
+                    k > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[stage]));
+          umma_commit(smem_u32(&tmem_full_bar[buf]));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+          if (++buf == Cfg::kTmemBufs) {
+            buf = 0;
+            bphase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4) {
+    // ---------------- promotion + store ----------------
+    const int ew = warp - 4;
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) belong to warps with this id mod 4
+    const int half = ew >> 2;      // which half of the tile's columns
+    const int row_in_tile = quarter * 32 + lane;
+    const int col_base = half * Cfg::kColsPerThread;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int epi_tid = static_cast<int>(threadIdx.x) - 128;
+
+    int buf = 0;
+    uint32_t bphase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      const WorkItem it = decode_work(p, w, BN);
+      const int row = it.m0 + row_in_tile;
+      const int row_ld = min(row, p.M - 1);
+      const float* as_ptr = p.a_scale + static_cast<long long>(row_ld) * p.sa_m;
+      // b_scale rows this thread's columns can touch (at most 2 for <= 128 columns).
+      const int gcol0 = it.n0 + col_base + p.n_phase;
+      const int jb0 = gcol0 >> 7;
+      const int jb_lo = min(jb0, p.b_scale_rows - 1);
+      const int jb_hi = min(jb0 + 1, p.b_scale_rows - 1);
+      const float* bs_lo = p.b_scale + static_cast<long long>(jb_lo) * p.sb_n;
+      const float* bs_hi = p.b_scale + static_cast<long long>(jb_hi) * p.sb_n;
+
+      float2 acc[Cfg::kColsPerThread / 2];
+#pragma unroll
+      for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+
+      float a_s = __ldg(as_ptr + static_cast<long long>(it.kb_begin) * p.sa_k);
+      float b_lo = __ldg(bs_lo + static_cast<long long>(it.kb_begin) * p.sb_k);
+      float b_hi = __ldg(bs_hi + static_cast<long long>(it.kb_begin) * p.sb_k);
+
+      for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+        const float s_lo = a_s * b_lo;
+        const float s_hi = a_s * b_hi;
+        if (kb + 1 < it.kb_end) {
+          a_s = __ldg(as_ptr + static_cast<long long>(kb + 1) * p.sa_k);
+          b_lo = __ldg(bs_lo + static_cast<long long>(kb + 1) * p.sb_k);
+          b_hi = __ldg(bs_hi + static_cast<long long>(kb + 1) * p.sb_k);
+        }
+        if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), bphase, ctx, 0x400 | buf)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(buf * BN + col_base);
+        uint32_t v[2][32];
+        tmem_ld_32x32(taddr, v[0]);
+#pragma unroll
+        for (int ch = 0; ch < Cfg::kChunks; ++ch) {
+          tmem_ld_wait(v[ch & 1]);
+          if (ch + 1 < Cfg::kChunks) {
+            tmem_ld_32x32(taddr + static_cast<uint32_t>((ch + 1) * 32), v[(ch + 1) & 1]);
+          } else {
+            // Every column of this buffer is in registers: hand it back to the MMA warp.
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+          }
+          const float s = (((gcol0 + ch * 32) >> 7) == jb0) ? s_lo : s_hi;
+          const float2 s2 = make_float2(s, s);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) fma2(acc[ch * 16 + j], v[ch & 1][2 * j], v[ch & 1][2 * j + 1], s2);
+        }
+        if (++buf == Cfg::kTmemBufs) {
+          buf = 0;
+          bphase ^= 1u;
+        }
+      }
+      if (!ok) break;
+
+      const int col0 = it.n0 + col_base;  // first column of this thread inside (the shard of) c
+      if (p.split_k == 1) {
+        if (row < p.M) {
+          __nv_bfloat16* crow = p.c + static_cast<long long>(row) * p.ldc;
+#pragma unroll
+          for (int j = 0; j < Cfg::kColsPerThread / 8; ++j) {
+            const int col = col0 + j * 8;
+            if (p.vec_store && col + 8 <= p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(acc[j * 4 + 0].x, acc[j * 4 + 0].y);
+              o.y = pack_bf16x2(acc[j * 4 + 1].x, acc[j * 4 + 1].y);
+              o.z = pack_bf16x2(acc[j * 4 + 2].x, acc[j * 4 + 2].y);
+              o.w = pack_bf16x2(acc[j * 4 + 3].x, acc[j * 4 + 3].y);
+              *reinterpret_cast<uint4*>(crow + col) = o;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (col + 2 * e < p.N) crow[col + 2 * e] = __float2bfloat16_rn(acc[j * 4 + e].x);
+                if (col + 2 * e + 1 < p.N) crow[col + 2 * e + 1] = __float2bfloat16_rn(acc[j * 4 + e].y);
+              }
+            }
+          }
+        }
+      } else {
+        // Split-K: publish this K range's fp32 tile, then the last CTA to arrive for the tile
+        // sums the ranges in order 0..split_k-1 (so the result does not depend on arrival order).
+        // Plane layout per (tile, split): float4 index (col/4)*128 + row, so that a warp's store
+        // covers 512 contiguous bytes.
+        const size_t plane_floats = static_cast<size_t>(kBlockM) * BN;
+        float4* mine = reinterpret_cast<float4*>(p.partials +
+                                                 (static_cast<size_t>(it.tile) * p.split_k + it.split) * plane_floats);
+#pragma unroll
+        for (int j = 0; j < Cfg::kColsPerThread / 4; ++j) {
+          const int c4 = (col_base >> 2) + j;
+          mine[c4 * kBlockM + row_in_tile] =
+              make_float4(acc[2 * j].x, acc[2 * j].y, acc[2 * j + 1].x, acc[2 * j + 1].y);
+        }
+        __threadfence();
+        epi_bar_sync();
+        if (epi_tid == 0) {
+          const int prev = atomicAdd(p.counters + it.tile, 1);
+          const int last = (prev == p.split_k - 1) ? 1 : 0;
+          if (last) p.counters[it.tile] = 0;  // leave the counters zero for the next launch
+          *last_flag = last;
+        }
+        epi_bar_sync();
+        const int is_last = *last_flag;
+        epi_bar_sync();  // everyone has read the flag before thread 0 can overwrite it
+        if (is_last) {
+          __threadfence();
+          const float4* base =
+              reinterpret_cast<const float4*>(p.partials + static_cast<size_t>(it.tile) * p.split_k * plane_floats);
+          if (row < p.M) {
+            __nv_bfloat16* crow = p.c + static_cast<long long>(row) * p.ldc;
+#pragma unroll 2
+            for (int j = 0; j < Cfg::kColsPerThread / 4; ++j) {
+              const int c4 = (col_base >> 2) + j;
+              float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int s = 0; s < p.split_k; ++s) {
+                const float4 t = __ldcg(base + static_cast<size_t>(s) * (plane_floats / 4) + c4 * kBlockM + row_in_tile);
+                sum.x += t.x;
+                sum.y += t.y;
+                sum.z += t.z;
+                sum.w += t.w;
+              }
+              const int col = col0 + j * 4;
+              if (p.vec_store && col + 4 <= p.N) {
+                uint2 o;
+                o.x = pack_bf16x2(sum.x, sum.y);
+                o.y = pack_bf16x2(sum.z, sum.w);
+                *reinterpret_cast<uint2*>(crow + col) = o;
+              } else {
+                if (col + 0 < p.N) crow[col + 0] = __float2bfloat16_rn(sum.x);
+                if (col + 1 < p.N) crow[col + 1] = __float2bfloat16_rn(sum.y);
+                if (col + 2 < p.N) crow[col + 2] = __float2bfloat16_rn(sum.z);
+                if (col + 3 < p.N) crow[col + 3] = __float2bfloat16_rn(sum.w);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // Teardown: every role has left its loop (normally or through an expired wait).
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      return nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// e4m3 matrix [rows, K] with K contiguous, box = 128 bytes of K x box_rows rows, 128-byte swizzle.
+bool encode_operand_map(CUtensorMap* map, const void* base, int rows, int K, long long ld, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+int smem_bytes_for(int block_n, int stages) {
+  const int stage = kBlockM * kBlockK + block_n * kBlockK;
+  return stages * stage + 1024 /* alignment slack */ + 256 /* barriers and flags */;
+}
+
+constexpr int kMaxSmem = 232448;  // 227 KiB opt-in limit per CTA on sm_100
+
+int max_stages_for(int block_n) {
+  int s = 8;
+  while (s > 2 && smem_bytes_for(block_n, s) > kMaxSmem) --s;
+  return s;
+}
+
+bool valid_block_n(int bn) { return bn == 64 || bn == 128 || bn == 192 || bn == 256; }
+
+size_t plan_workspace_bytes(const b200_fp8_mm_plan& pl) {
+  if (pl.split_k <= 1) return 0;
+  return static_cast<size_t>(kCounterBytes) +
+         static_cast<size_t>(pl.tiles) * pl.split_k * kBlockM * pl.block_n * sizeof(float);
+}
+
+// Tile/launch selection: a pure function of the problem and the SM count.
+void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forced, b200_fp8_mm_plan* out) {
+  const int kblocks = K / kBlockK;
+  const int tiles_m = ceil_div(M, kBlockM);
+  int bn = (forced && forced->block_n) ? forced->block_n : 0;
+  int split = (forced && forced->split_k) ? forced->split_k : 0;
+  if (bn == 0) {
+    // Fewest, largest tiles that still fill the machine; then the least padded width.
+    const int cands[4] = {256, 192, 128, 64};
+    double best = 1e30;
+    for (int i = 0; i < 4; ++i) {
+      const int c = cands[i];
+      const int tiles = tiles_m * ceil_div(N, c);
+      const int waves = ceil_div(tiles, sm_count);
+      // Cost model in MMA clocks per K block: time of a 128 x c block on the tensor pipe, floored by
+      // the shared-memory operand traffic (128 B/clk) of a 128 x c x 32 instruction.
+      const double mma = c / 64.0 * 128.0;
+      const double smem = (kBlockM + c) * 128.0 / 128.0;
+      const double per_block = mma > smem ? mma : smem;
+      const double cost = waves * (per_block * kblocks + 600.0 + 4.0 * c);
+      if (cost < best - 1e-9) {
+        best = cost;
+        bn = c;
+      }
+    }
+  }
+  const int tiles_n = ceil_div(N, bn);
+  const int tiles = tiles_m * tiles_n;
+  if (split == 0) {
+    split = 1;
+    if (tiles * 2 <= sm_count && kblocks >= 8 && tiles <= kMaxCounters) {
+      split = sm_count / tiles;
+      const int max_split = kblocks / 4;
+      if (split > max_split) split = max_split;
+      if (split > 16) split = 16;
+      if (split < 1) split = 1;
+    }
+  }
+  int stages = (forced && forced->stages) ? forced->stages : max_stages_for(bn);
+  out->block_m = kBlockM;
+  out->block_n = bn;
+  out->cta_pair = 0;
+  out->split_k = split;
+  out->stages = stages;
+  out->tiles = tiles;
+  const int work = tiles * split;
+  out->grid = work < sm_count ? work : sm_count;
+  out->smem_bytes = smem_bytes_for(bn, stages);
+}
+
+bool plan_is_supported(const b200_fp8_mm_plan& pl, int kblocks) {
+  if (!valid_block_n(pl.block_n)) return false;
+  if (pl.cta_pair != 0) return false;
+  if (pl.stages < 2 || pl.stages > 8) return false;
+  if (pl.smem_bytes > kMaxSmem) return false;
+  if (pl.split_k < 1 || pl.split_k > kblocks) return false;
+  if (pl.split_k > 1 && pl.tiles > kMaxCounters) return false;
+  return true;
+}
+
+typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const KernelParams);
+
+template <int BN>
+KernelFn kernel_for_stages(int stages) {
+  switch (stages) {
+    case 2: return fp8_mm_blockscaled_kernel<BN, 2>;
+    case 3: return fp8_mm_blockscaled_kernel<BN, 3>;
+    case 4: return fp8_mm_blockscaled_kernel<BN, 4>;
+    case 5: return fp8_mm_blockscaled_kernel<BN, 5>;
+    case 6: return fp8_mm_blockscaled_kernel<BN, 6>;
+    case 7: return fp8_mm_blockscaled_kernel<BN, 7>;
+    case 8: return fp8_mm_blockscaled_kernel<BN, 8>;
+    default: return nullptr;
+  }
+}
+
+KernelFn kernel_for(int block_n, int stages) {
+  switch (block_n) {
+    case 64: return kernel_for_stages<64>(stages);
+    case 128: return kernel_for_stages<128>(stages);
+    case 192: return kernel_for_stages<192>(stages);
+    case 256: return kernel_for_stages<256>(stages);
+    default: return nullptr;
+  }
+}
+
+int device_sm_count() {
+  // Cached per process for the current device at first use; B200 has 148.
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0, major = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
+    if (major != 10) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int run(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int M, int N, int K,
+        long long lda, long long ldb, long long sa_m, long long sa_k, long long sb_n, long long sb_k, long long ldc,
+        int n_phase, void* workspace, size_t workspace_bytes, int* device_status, void* stream,
+        const b200_fp8_mm_plan* forced) {
+  if (a == nullptr || b == nullptr || a_scale == nullptr || b_scale == nullptr || c == nullptr)
+    return B200_FP8_MM_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return B200_FP8_MM_ERR_SHAPE;
+  if (lda < K || ldb < K || (lda % 16) != 0 || (ldb % 16) != 0 || ldc < N) return B200_FP8_MM_ERR_STRIDE;
+  if ((reinterpret_cast<uintptr_t>(a) % 16) != 0 || (reinterpret_cast<uintptr_t>(b) % 16) != 0)
+    return B200_FP8_MM_ERR_ALIGN;
+  if (n_phase < 0 || n_phase >= 128 || (n_phase % 32) != 0) return B200_FP8_MM_ERR_PHASE;
+
+  const int sm_count = device_sm_count();
+  if (sm_count <= 0) return B200_FP8_MM_ERR_DRIVER;
+
+  b200_fp8_mm_plan pl;
+  choose_plan(M, N, K, sm_count, forced, &pl);
+  if (forced && forced->cta_pair) pl.cta_pair = forced->cta_pair;
+  const int kblocks = K / kBlockK;
+  if (!plan_is_supported(pl, kblocks)) return B200_FP8_MM_ERR_PLAN;
+  const size_t need = plan_workspace_bytes(pl);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need ||
+                   (reinterpret_cast<uintptr_t>(workspace) % 256) != 0))
+    return B200_FP8_MM_ERR_WORKSPACE;
+
+  KernelFn fn = kernel_for(pl.block_n, pl.stages);
+  if (fn == nullptr) return B200_FP8_MM_ERR_PLAN;
+
+  CUtensorMap map_a, map_b;
+  if (!encode_operand_map(&map_a, a, M, K, lda, kBlockM)) return B200_FP8_MM_ERR_DRIVER;
+  if (!encode_operand_map(&map_b, b, N, K, ldb, pl.block_n)) return B200_FP8_MM_ERR_DRIVER;
+
+  KernelParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.a_scale = a_scale;
+  kp.b_scale = b_scale;
+  kp.c = static_cast<__nv_bfloat16*>(c);
+  kp.counters = static_cast<int*>(workspace);
+  kp.partials = need > 0 ? reinterpret_cast<float*>(static_cast<char*>(workspace) + kCounterBytes) : nullptr;
+  kp.status = device_status;
+  kp.sa_m = sa_m;
+  kp.sa_k = sa_k;
+  kp.sb_n = sb_n;
+  kp.sb_k = sb_k;
+  kp.ldc = ldc;
+  kp.M = M;
+  kp.N = N;
+  kp.K = K;
+  kp.n_phase = n_phase;
+  kp.tiles_m = ceil_div(M, kBlockM);
+  kp.tiles_n = ceil_div(N, pl.block_n);
+  kp.split_k = pl.split_k;
+  kp.kblocks = kblocks;
+  kp.raster_group = 8;
+  kp.b_scale_rows = ceil_div(N + n_phase, 128);
+  kp.vec_store =
+      ((reinterpret_cast<uintptr_t>(c) % 16) == 0 && (ldc % 8) == 0 && (N % 8) == 0) ? 1 : 0;
+
+  cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_FP8_MM_ERR_LAUNCH;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(pl.grid), 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(pl.smem_bytes);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  err = cudaLaunchKernelEx(&cfg, fn, map_a, map_b, kp);
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200_FP8_MM_ERR_LAUNCH;
+  }
+  return B200_FP8_MM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_fp8_mm(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int M, int N,
+                int K, long long lda, long long ldb, long long sa_m, long long sa_k, long long sb_n, long long sb_k,
+                long long ldc, int n_phase, void* workspace, size_t workspace_bytes, int* device_status,
+                void* stream) {
+  return run(a, b, a_scale, b_scale, c, M, N, K, lda, ldb, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, workspace,
+             workspace_bytes, device_status, stream, nullptr);
+}
+
+int b200_fp8_mm_planned(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int M,
+                        int N, int K, long long lda, long long ldb, long long sa_m, long long sa_k, long long sb_n,
+                        long long sb_k, long long ldc, int n_phase, void* workspace, size_t workspace_bytes,
+                        int* device_status, void* stream, const b200_fp8_mm_plan* forced) {
+  return run(a, b, a_scale, b_scale, c, M, N, K, lda, ldb, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, workspace,
+             workspace_bytes, device_status, stream, forced);
+}
+
+size_t b200_fp8_mm_workspace_bytes(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return 0;
+  b200_fp8_mm_plan pl;
+  choose_plan(M, N, K, 148, nullptr, &pl);
+  const size_t need = plan_workspace_bytes(pl);
+  return ((need + 255) / 256) * 256;
+}
+
+size_t b200_fp8_mm_plan_workspace_bytes(int M, int N, int K, const b200_fp8_mm_plan* forced) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return 0;
+  b200_fp8_mm_plan pl;
+  choose_plan(M, N, K, 148, forced, &pl);
+  const size_t need = plan_workspace_bytes(pl);
+  return ((need + 255) / 256) * 256;
+}
+
+int b200_fp8_mm_describe(int M, int N, int K, int n_phase, int sm_count, b200_fp8_mm_plan* out) {
+  if (out == nullptr) return B200_FP8_MM_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return B200_FP8_MM_ERR_SHAPE;
+  if (n_phase < 0 || n_phase >= 128 || (n_phase % 32) != 0) return B200_FP8_MM_ERR_PHASE;
+  choose_plan(M, N, K, sm_count > 0 ? sm_count : 148, nullptr, out);
+  return B200_FP8_MM_OK;
+}
+
+const char* b200_fp8_mm_strerror(int code) {
+  switch (code) {
+    case B200_FP8_MM_OK: return "ok";
+    case B200_FP8_MM_ERR_NULL: return "a required pointer is NULL";
+    case B200_FP8_MM_ERR_SHAPE: return "bad shape: M, N, K must be positive and K a multiple of 128";
+    case B200_FP8_MM_ERR_STRIDE: return "unsupported stride: a and b need K contiguous, row strides multiples of 16";
+    case B200_FP8_MM_ERR_ALIGN: return "a and b must be 16-byte aligned";
+    case B200_FP8_MM_ERR_PHASE: return "n_phase must be 0, 32, 64 or 96";
+    case B200_FP8_MM_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case B200_FP8_MM_ERR_PLAN: return "forced plan not supported";
+    case B200_FP8_MM_ERR_DRIVER: return "no sm_100 device or tensor-map encode failed";
+    case B200_FP8_MM_ERR_LAUNCH: return "kernel launch failed";
+    default: return "unknown error";
+  }
+}
+
+int b200_fp8_mm_abi_version(void) { return 1; }
+
+}  // extern "C"

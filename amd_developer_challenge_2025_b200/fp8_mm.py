@@ -1,0 +1,178 @@
+"""Host side of the operator: argument checks, workspace cache, the C-ABI call.
+
+Mirrors the reference's pybind launcher `fp8_mm(a, b, as, bs, c, c_tmp)`
+(1-amd-fp8-mm/amd-fp8-mm-submission.py:514-579) with the checks it lacks."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+SCALE_BLOCK = 128
+
+
+@dataclass(frozen=True)
+class Plan:
+    block_m: int = 0
+    block_n: int = 0
+    cta_pair: int = 0
+    split_k: int = 0
+    stages: int = 0
+    grid: int = 0
+    tiles: int = 0
+    smem_bytes: int = 0
+
+    def to_c(self) -> _lib.CPlan:
+        return _lib.CPlan(self.block_m, self.block_n, self.cta_pair, self.split_k, self.stages, self.grid,
+                          self.tiles, self.smem_bytes)
+
+    @staticmethod
+    def from_c(c: _lib.CPlan) -> "Plan":
+        return Plan(c.block_m, c.block_n, c.cta_pair, c.split_k, c.stages, c.grid, c.tiles, c.smem_bytes)
+
+
+class Fp8MmError(RuntimeError):
+    def __init__(self, code: int, what: str = ""):
+        self.code = code
+        super().__init__(f"b200_fp8_mm error {code}: {_lib.strerror(code)}{(' (' + what + ')') if what else ''}")
+
+
+class Fp8MmDeviceError(RuntimeError):
+    """A bounded wait inside the kernel expired; the output is not valid."""
+
+
+def describe(m: int, n: int, k: int, n_phase: int = 0, sm_count: int = 0) -> Plan:
+    """The tile/launch plan the library picks for this problem (host arithmetic only)."""
+    out = _lib.CPlan()
+    rc = _lib.load().b200_fp8_mm_describe(m, n, k, n_phase, sm_count, ctypes.byref(out))
+    if rc != 0:
+        raise Fp8MmError(rc)
+    return Plan.from_c(out)
+
+
+def workspace_bytes(m: int, n: int, k: int, plan: Plan | None = None) -> int:
+    lib = _lib.load()
+    if plan is None:
+        return int(lib.b200_fp8_mm_workspace_bytes(m, n, k))
+    cp = plan.to_c()
+    return int(lib.b200_fp8_mm_plan_workspace_bytes(m, n, k, ctypes.byref(cp)))
+
+
+# Per-device scratch owned by the Python side: the library itself allocates nothing. The
+# reference allocates its split-K scratch on every call
+# (1-amd-fp8-mm/amd-fp8-mm-submission.py:600); here it is cached and only ever grows.
+_workspaces: dict[int, torch.Tensor] = {}
+_status: dict[int, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
+    if nbytes == 0:
+        return None
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[idx] = ws
+    return ws
+
+
+def _status_words(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _status.get(idx)
+    if st is None:
+        st = torch.zeros(4, dtype=torch.int32, device=device)
+        _status[idx] = st
+    return st
+
+
+def _check(cond: bool, msg: str):
+    if not cond:
+        raise ValueError(msg)
+
+
+def fp8_mm(a, b, a_scale, b_scale, c, n_phase: int = 0, plan: Plan | None = None, check: bool = False):
+    """c[M,N] (bf16) = block-scaled a[M,K] @ b[N,K]^T on the current CUDA stream; returns c.
+
+    a, b: float8_e4m3fn with K contiguous. a_scale: fp32 [M, K/128], any strides.
+    b_scale: fp32 [ceil((N+n_phase)/128), K/128], any strides. `n_phase`: offset of b's first
+    row inside its 128-row scale block (0 unless b is a column shard of a larger matrix).
+    `plan`: force tile parameters (sweeps/tests). `check`: synchronise and raise if a wait
+    inside the kernel expired. Asynchronous otherwise, like the reference's launcher."""
+    lib = _lib.load()
+    _check(a.is_cuda and b.is_cuda and a_scale.is_cuda and b_scale.is_cuda and c.is_cuda,
+           "all five tensors must be CUDA tensors (there is no CPU path)")
+    _check(a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn, "a and b must be float8_e4m3fn")
+    _check(a_scale.dtype == torch.float32 and b_scale.dtype == torch.float32, "scales must be float32")
+    _check(c.dtype == torch.bfloat16, "c must be bfloat16")
+    _check(a.dim() == 2 and b.dim() == 2 and c.dim() == 2, "a, b, c must be 2-D")
+    m, k = a.shape
+    n = b.shape[0]
+    _check(b.shape[1] == k, "a and b disagree on K")
+    _check(tuple(c.shape) == (m, n), "c must be [M, N]")
+    _check(k % SCALE_BLOCK == 0, "K must be a multiple of 128")
+    kb = k // SCALE_BLOCK
+    nb = (n + n_phase + SCALE_BLOCK - 1) // SCALE_BLOCK
+    _check(tuple(a_scale.shape) == (m, kb), f"a_scale must be [{m}, {kb}]")
+    _check(tuple(b_scale.shape) == (nb, kb), f"b_scale must be [{nb}, {kb}]")
+    _check(a.stride(1) == 1 and b.stride(1) == 1,
+           "a and b must have K contiguous (M-major/N-major storage is not supported yet)")
+    _check(c.stride(1) == 1, "c must have N contiguous")
+    dev = a.device
+    _check(all(t.device == dev for t in (b, a_scale, b_scale, c)), "tensors on different devices")
+
+    nbytes = workspace_bytes(m, n, k, plan)
+    ws = _workspace(dev, nbytes)
+    st = _status_words(dev)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        args = [
+            a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), c.data_ptr(),
+            m, n, k,
+            a.stride(0), b.stride(0),
+            a_scale.stride(0), a_scale.stride(1),
+            b_scale.stride(0), b_scale.stride(1),
+            c.stride(0), n_phase,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            st.data_ptr(), stream,
+        ]
+        if plan is None:
+            rc = lib.b200_fp8_mm(*args)
+        else:
+            cp = plan.to_c()
+            rc = lib.b200_fp8_mm_planned(*args, ctypes.byref(cp))
+    if rc != 0:
+        raise Fp8MmError(rc, f"M={m} N={n} K={k}")
+    if check:
+        check_device_status(dev)
+    return c
+
+
+def check_device_status(device=None):
+    """Synchronises and raises Fp8MmDeviceError if any launch since the last check gave up a wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    torch.cuda.synchronize(dev)
+    st = _status_words(dev)
+    words = st.tolist()
+    if words[0] != 0:
+        st.zero_()
+        ws = _workspaces.get(dev.index if dev.index is not None else torch.cuda.current_device())
+        if ws is not None:
+            ws[:4096].zero_()  # split-K counters may be mid-count after an aborted launch
+        raise Fp8MmDeviceError(
+            f"kernel wait expired: code={words[0]} where=0x{words[1]:x} block={words[2]} parity={words[3]}")
+
+
+def fp8_mm_host(a, b, a_scale, b_scale, c, device="cuda", n_phase: int = 0):
+    """The same operator for HOST tensors: copies the four inputs to `device`, runs the GEMM,
+    copies c back into the caller's host tensor and returns it. This is the call the end-to-end
+    benchmark times (host<->device copies inside)."""
+    dev = torch.device(device)
+    da, db, das, dbs = (t.to(dev, non_blocking=True) for t in (a, b, a_scale, b_scale))
+    dc = torch.empty(c.shape, dtype=torch.bfloat16, device=dev)
+    fp8_mm(da, db, das, dbs, dc, n_phase=n_phase)
+    c.copy_(dc, non_blocking=True)
+    torch.cuda.current_stream(dev).synchronize()
+    return c

@@ -1,0 +1,134 @@
+/*
+ * C ABI of the B200 (sm_100a) FP8 block-scaled GEMM library, libb200fp8mm.so.
+ *
+ * The operator computed is the one behind the reference's
+ * `custom_kernel((a, b, a_scale, b_scale, c)) -> c`
+ * (1-amd-fp8-mm/amd-fp8-mm-submission.py:594-604):
+ *
+ *   c[i,j] = bf16( sum_kb ( sum_{kk in 128-block kb} a[i,kk]*b[j,kk] )
+ *                        * a_scale[i,kb] * b_scale[(j + n_phase)/128, kb] )
+ *
+ * with a, b in e4m3fn, the inner sum accumulated in fp32 from zero by the
+ * tensor cores, and the scaled blocks accumulated in fp32
+ * (1-amd-fp8-mm/amd-fp8-mm-submission.py:302-357 is the reference loop).
+ *
+ * Every entry point takes plain pointers and sizes. The library owns no device
+ * memory and allocates none; the caller supplies the workspace.
+ */
+#ifndef B200_FP8_MM_H_
+#define B200_FP8_MM_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Return codes. 0 is success; everything else means no kernel was launched,
+ * except B200_FP8_MM_ERR_LAUNCH (the launch itself failed). */
+enum {
+  B200_FP8_MM_OK = 0,
+  B200_FP8_MM_ERR_NULL = 1,        /* a required pointer is NULL                   */
+  B200_FP8_MM_ERR_SHAPE = 2,       /* M, N or K <= 0, or K not a multiple of 128   */
+  B200_FP8_MM_ERR_STRIDE = 3,      /* a stride the TMA path cannot address         */
+  B200_FP8_MM_ERR_ALIGN = 4,       /* a or b not 16-byte aligned                   */
+  B200_FP8_MM_ERR_PHASE = 5,       /* n_phase outside [0,128) or not a multiple of 32 */
+  B200_FP8_MM_ERR_WORKSPACE = 6,   /* workspace missing or too small for the plan  */
+  B200_FP8_MM_ERR_PLAN = 7,        /* a forced plan is not one the kernels support */
+  B200_FP8_MM_ERR_DRIVER = 8,      /* tensor-map encode failed / no sm_100 device  */
+  B200_FP8_MM_ERR_LAUNCH = 9       /* cudaLaunchKernelEx returned an error         */
+};
+
+/* Device-side status word values (written to device_status[0]; [1] holds the
+ * role and barrier that gave up, [2] the block index). A kernel never traps and
+ * never spins without limit: a wait that expires records one of these and every
+ * role leaves its loop. */
+enum {
+  B200_FP8_MM_DEV_OK = 0,
+  B200_FP8_MM_DEV_WAIT_EXPIRED = 1
+};
+
+/* Tile and launch parameters chosen for one problem. Replaces the reference's
+ * exact-shape dispatch table (1-amd-fp8-mm/amd-fp8-mm-submission.py:528-578)
+ * and its older size heuristic (1-amd-fp8-mm/1-amd-fp8-mm-original.py:484-514). */
+typedef struct b200_fp8_mm_plan {
+  int block_m;    /* rows of C per CTA (128)                                        */
+  int block_n;    /* columns of C per tile: 64, 128, 192 or 256                     */
+  int cta_pair;   /* 1: two CTAs share a 256-row tile through cta_group::2          */
+  int split_k;    /* number of K ranges per tile (1 = no split)                     */
+  int stages;     /* depth of the TMA -> shared memory ring                         */
+  int grid;       /* CTAs launched (persistent; a multiple of 2 when cta_pair)      */
+  int tiles;      /* output tiles (x split_k = work items)                          */
+  int smem_bytes; /* dynamic shared memory per CTA                                  */
+} b200_fp8_mm_plan;
+
+/*
+ * The GEMM. Replaces the pybind launcher `fp8_mm(a, b, as, bs, c, c_tmp)`
+ * (1-amd-fp8-mm/amd-fp8-mm-submission.py:8, 514-579).
+ *
+ *  a        e4m3fn [M,K], element (i,kk) at a + i*lda + kk   (K contiguous)
+ *  b        e4m3fn [N,K], element (j,kk) at b + j*ldb + kk
+ *  a_scale  fp32, element (i,kb)  at a_scale + i*sa_m + kb*sa_k
+ *  b_scale  fp32, element (jb,kb) at b_scale + jb*sb_n + kb*sb_k, with
+ *           jb = (j + n_phase)/128: n_phase is the offset of column 0 of this
+ *           (shard of) b inside its 128-column scale block, 0 for a whole matrix
+ *  c        bf16 [M,N], element (i,j) at c + i*ldc + j; written, never read
+ *  lda, ldb multiples of 16; a and b 16-byte aligned (TMA rules)
+ *  workspace / workspace_bytes
+ *           at least b200_fp8_mm_workspace_bytes(M,N,K) bytes (for a forced plan:
+ *           b200_fp8_mm_plan_workspace_bytes), 256-byte aligned;
+ *           its first 4096 bytes must be zero before the first call and are left
+ *           zero by every call. May be NULL when that function returns 0.
+ *  device_status  int[4] in device memory, zeroed by the caller; see the enum above
+ *  stream   a cudaStream_t (NULL = the legacy default stream, as the reference's
+ *           `<<<grid, block, 0, 0>>>` launches use)
+ *
+ * Asynchronous like the reference: returns after the launch. Inputs are const
+ * and are never written (the reference's pre-transpose path overwrites a and b,
+ * 1-amd-fp8-mm/amd-fp8-mm-submission.py:152).
+ */
+int b200_fp8_mm(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c,
+                int M, int N, int K,
+                long long lda, long long ldb,
+                long long sa_m, long long sa_k,
+                long long sb_n, long long sb_k,
+                long long ldc, int n_phase,
+                void* workspace, size_t workspace_bytes,
+                int* device_status, void* stream);
+
+/* Same, with the plan given by the caller (block_n, cta_pair, split_k, stages
+ * are read; 0 in any of them means "choose"). Used for sweeps and by the tests
+ * to force every kernel variant. */
+int b200_fp8_mm_planned(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c,
+                        int M, int N, int K,
+                        long long lda, long long ldb,
+                        long long sa_m, long long sa_k,
+                        long long sb_n, long long sb_k,
+                        long long ldc, int n_phase,
+                        void* workspace, size_t workspace_bytes,
+                        int* device_status, void* stream,
+                        const b200_fp8_mm_plan* forced);
+
+/* Workspace the plan chosen by b200_fp8_mm for (M,N,K) needs, in bytes (0 when it does
+ * not split K). Replaces
+ * the reference's per-call `torch.empty(m*n*4)` split-K scratch
+ * (1-amd-fp8-mm/amd-fp8-mm-submission.py:597-601). */
+size_t b200_fp8_mm_workspace_bytes(int M, int N, int K);
+
+/* Workspace a forced plan needs (0 fields in *forced mean "choose"), rounded up to 256. */
+size_t b200_fp8_mm_plan_workspace_bytes(int M, int N, int K, const b200_fp8_mm_plan* forced);
+
+/* Fills *out with the plan b200_fp8_mm would use for this problem on a GPU with
+ * sm_count SMs (0 = 148). Pure host arithmetic; needs no GPU. */
+int b200_fp8_mm_describe(int M, int N, int K, int n_phase, int sm_count, b200_fp8_mm_plan* out);
+
+/* Text for a return code. */
+const char* b200_fp8_mm_strerror(int code);
+
+/* Library version, bumped when the ABI changes. */
+int b200_fp8_mm_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_FP8_MM_H_ */

@@ -1,0 +1,99 @@
+"""CPU tests of the host side: the C-ABI library loads and exports what the header declares,
+argument errors come back as codes without any launch, and the tile selector is sane."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "b200_fp8_mm.h")
+
+
+def header_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_fp8_mm\w*)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    from amd_developer_challenge_2025_b200 import _lib
+
+    lib = ctypes.CDLL(built_library)
+    declared = header_functions()
+    assert "b200_fp8_mm" in declared and "b200_fp8_mm_describe" in declared
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert sorted(_lib.EXPORTS) == [d for d in declared if d in _lib.EXPORTS]
+    assert set(declared) <= set(_lib.EXPORTS) | {"b200_fp8_mm_plan"}
+    assert _lib.load().b200_fp8_mm_abi_version() == _lib.ABI_VERSION
+
+
+def test_error_codes_without_launch(built_library):
+    from amd_developer_challenge_2025_b200 import _lib
+
+    lib = _lib.load()
+    one = ctypes.c_void_p(4096)  # never dereferenced: every check below fails first
+
+    def call(a=one, b=one, a_s=one, b_s=one, c=one, m=128, n=128, k=128, lda=None, ldb=None, ldc=None, phase=0):
+        return lib.b200_fp8_mm(a, b, a_s, b_s, c, m, n, k, lda or k, ldb or k, k // 128 or 1, 1, k // 128 or 1, 1,
+                               ldc or n, phase, None, 0, None, None)
+
+    assert call(a=None) == 1 and call(c=None) == 1
+    assert call(k=100) == 2 and call(m=0) == 2 and call(n=-5) == 2
+    assert call(lda=130) == 3 and call(ldb=64) == 3 and call(ldc=64) == 3
+    assert call(a=ctypes.c_void_p(4100)) == 4
+    assert call(phase=128) == 5 and call(phase=16) == 5 and call(phase=-32) == 5
+    for code in range(0, 10):
+        assert len(_lib.strerror(code)) > 0
+    assert "unknown" in _lib.strerror(99)
+
+
+def test_python_wrapper_rejects_cpu_tensors_and_bad_shapes(built_library):
+    import amd_developer_challenge_2025_b200 as pkg
+
+    a, b, a_s, b_s, c = pkg.make_inputs(8, 128, 128, seed=1)
+    with pytest.raises(ValueError, match="CUDA"):
+        pkg.custom_kernel((a, b, a_s, b_s, c))
+
+
+def test_selector_is_pure_and_sane(built_library):
+    import amd_developer_challenge_2025_b200 as pkg
+
+    shapes = [(m, n, k) for m in (256, 512, 2048, 8192, 16384)
+              for (n, k) in ((1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168),
+                             (7168, 2304), (512, 7168), (4096, 512))]
+    for (m, n, k) in shapes:
+        p1, p2 = pkg.describe(m, n, k), pkg.describe(m, n, k)
+        assert p1 == p2
+        assert p1.block_m == 128 and p1.block_n in (64, 128, 192, 256)
+        assert 1 <= p1.split_k <= k // 128
+        assert 2 <= p1.stages <= 8 and p1.smem_bytes <= 232448
+        tiles = -(-m // (p1.block_m * (2 if p1.cta_pair else 1))) * -(-n // p1.block_n)
+        assert p1.tiles == tiles
+        assert 1 <= p1.grid <= 148 and p1.grid <= tiles * p1.split_k * (2 if p1.cta_pair else 1)
+        ws = pkg.workspace_bytes(m, n, k)
+        assert (ws == 0) == (p1.split_k == 1)
+        if p1.split_k > 1:
+            assert ws >= 4096 + p1.tiles * p1.split_k * 128 * p1.block_n * 4
+    with pytest.raises(Exception):
+        pkg.describe(128, 128, 100)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from amd_developer_challenge_2025_b200 import _lib
+
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError, match="no CPU fallback"):
+        _lib.load()
+
+
+def test_product_never_imports_oracle():
+    pkg_dir = os.path.join(ROOT, "amd_developer_challenge_2025_b200")
+    for dirpath, _, files in os.walk(pkg_dir):
+        for f in files:
+            if f.endswith((".py", ".cu", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("oracle and", "").replace("CPU oracle", ""), f
