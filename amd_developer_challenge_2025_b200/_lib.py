@@ -7,7 +7,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "lib", "libb200fp8mm.so")
+# B200_FP8_MM_LIB selects another build of the same library (e.g. one made with extra nvcc flags).
+LIB_PATH = os.environ.get("B200_FP8_MM_LIB") or os.path.join(HERE, "lib", "libb200fp8mm.so")
 
 ABI_VERSION = 1
 

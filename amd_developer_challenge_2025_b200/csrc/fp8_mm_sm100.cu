@@ -9,14 +9,23 @@
 // in fp32 on the vector ALU, and one fp32 -> bf16 rounding at the end.
 //
 // Structure of one CTA (384 threads, one CTA per SM, persistent over work items):
-//   warp 0      TMA producer: A (128 x 128 B) and B (BN x 128 B) tiles of one K block into a
-//               SWIZZLE_128B shared-memory ring, completion on an mbarrier per stage
+//   warp 0      TMA producer: A (128 x 128 B) and B tiles of one K block into a SWIZZLE_128B
+//               shared-memory ring, completion on an mbarrier per stage
 //   warp 1      MMA issuer: 4 x tcgen05.mma.kind::f8f6f4 (K=32 each) per K block into one of
 //               the TMEM partial buffers, tcgen05.commit to free the stage and publish the buffer
 //   warp 2      allocates / frees TMEM
+//   warp 3      scale loader: cp.async of the a_scale / b_scale values of FOUR K blocks at a time
+//               into a small shared-memory ring, up to 16 K blocks ahead
 //   warps 4-11  promotion + store: tcgen05.ld the partial, fma into register accumulators with
 //               the per-row, per-block scale, then bf16 stores (or split-K partials + last-arriver
 //               reduction)
+// While the tensor core streams operands, shared memory is nearly saturated and every
+// shared-memory operation of a warp (mbarrier probe, ld.shared) takes hundreds of clocks, so
+// the promotion warps touch shared memory as rarely as possible: one barrier wait and one
+// arrive per K block, and the scales of four K blocks fetched with three vector loads.
+// With PAIR, two CTAs of a cluster share one 256-row tile: each loads its own 128 rows of A and
+// half of the B rows, the leader CTA issues tcgen05.mma.cta_group::2 for both, and each CTA
+// promotes and stores its own 128 rows. No TMA load uses cluster multicast.
 // Every mbarrier wait is bounded: when it expires the kernel writes a status word and all roles
 // leave their loops; nothing traps and nothing spins without limit.
 
@@ -31,22 +40,30 @@
 
 namespace {
 
-constexpr int kBlockM = 128;
+constexpr int kBlockM = 128;  // rows of C per CTA
 constexpr int kBlockK = 128;  // bytes of e4m3 per row of a stage = one scale block = one 128B swizzle row
-constexpr int kUmmaK = 32;
+constexpr int kMmasPerBlock = 4;  // K = 32 per instruction
 constexpr int kNumEpiWarps = 8;
 constexpr int kNumEpiThreads = kNumEpiWarps * 32;
 constexpr int kNumThreads = 128 + kNumEpiThreads;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kCounterBytes = 4096;
 constexpr int kMaxCounters = kCounterBytes / 4;
+constexpr int kMaxStages = 8;
+constexpr int kScaleGroup = 4;                                   // K blocks per scale-ring slot
+constexpr int kScaleSlots = 4;                                   // ring depth (16 K blocks)
+constexpr int kScaleSlotFloats = kBlockM * kScaleGroup + 4 * kScaleGroup;  // a[128][4] + b[4][4]
+// Register split after setmaxnreg (light: producer / MMA / loader warps, heavy: promotion warps).
+// 128 * light + 256 * heavy = 384 * 168, the allocation the CTA is launched with.
+constexpr int kRegsLightWide = 40, kRegsHeavyWide = 232;  // block_n 256: 128 accumulators per thread
+constexpr int kRegsLight = 104, kRegsHeavy = 200;         // narrower tiles
 
 struct KernelParams {
   const float* a_scale;
   const float* b_scale;
   __nv_bfloat16* c;
   float* partials;  // split-K planes, tile-blocked
-  int* counters;    // one per output tile, zero between launches
+  int* counters;    // one per (tile, CTA of the pair), zero between launches
   int* status;      // may be null
   long long sa_m, sa_k, sb_n, sb_k, ldc;
   int M, N, K;
@@ -55,6 +72,7 @@ struct KernelParams {
   int raster_group;
   int b_scale_rows;
   int vec_store;  // 1 when c, ldc and N allow 16-byte stores
+  int stages;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -65,33 +83,60 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+// Arrive + expect_tx on a barrier given by its shared::cluster address (own CTA or the peer).
+// Default (CTA-scope release) semantics: a cluster-scope release here costs about 0.4 us per call.
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// One probe of the barrier. The suspend-time hint (nanoseconds) lets the hardware park the thread
+// until the phase completes instead of returning at once, so a waiting role costs few issue slots
+// and few shared-memory probes.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(200000)
       : "memory");
   return ok;
 }
 
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
 
@@ -102,20 +147,21 @@ struct AbortCtx {
 };
 
 // Bounded wait. Returns false when the wait expired here or in another role.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where) {
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                               int where) {
   const unsigned long long t0 = global_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xffu) == 0) {
-      if (*ctx.abort_flag) return false;
+    if ((++spins & 0x3u) == 0) {
+      if (*abort_flag) return false;
       if (global_ns() - t0 > kWaitLimitNs) {
-        *ctx.abort_flag = 1;
-        if (ctx.status != nullptr) {
-          if (atomicCAS(ctx.status, 0, B200_FP8_MM_DEV_WAIT_EXPIRED) == 0) {
-            ctx.status[1] = where;
-            ctx.status[2] = static_cast<int>(blockIdx.x);
-            ctx.status[3] = static_cast<int>(parity);
+        *abort_flag = 1;
+        if (status != nullptr) {
+          if (atomicCAS(status, 0, B200_FP8_MM_DEV_WAIT_EXPIRED) == 0) {
+            status[1] = where;
+            status[2] = static_cast<int>(blockIdx.x);
+            status[3] = static_cast<int>(parity);
           }
         }
         return false;
@@ -126,14 +172,35 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, ctx, where);
+  return mbar_wait_slow(bar, parity, ctx.abort_flag, ctx.status, where);
 }
 
+// TMA tile load into this CTA's shared memory; completion bytes go to `bar`.
+template <bool PAIR>
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
+  if constexpr (PAIR) {
+    // cta_group::2 form: the mbarrier may live in the peer CTA (the pair's leader).
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+  }
+}
+
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// The barrier receives one arrival from this thread when all its earlier cp.async have landed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void tcgen05_fence_before() {
@@ -143,23 +210,42 @@ __device__ __forceinline__ void tcgen05_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+template <bool PAIR>
 __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                         uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
+  if constexpr (PAIR) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
 }
 
+// Arrives on `bar` (same shared-memory offset in both CTAs of a pair) when all MMAs issued so
+// far by this thread have completed.
+template <bool PAIR>
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
+  if constexpr (PAIR) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"(static_cast<uint16_t>(3))
+        : "memory");
+  } else {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  }
 }
 
 // 32 lanes x 32 columns of fp32: thread t of the warp receives lane (base lane + t).
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -185,20 +271,66 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[32]) {
       : "memory");
 }
 
+// 64-column variants.
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]),
+        "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]),
+        "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]),
+        "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]),
+        "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[64]) {
+  asm volatile(
+      "tcgen05.wait::ld.sync.aligned;"
+      : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+        "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+        "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+        "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31]),
+        "+r"(v[32]), "+r"(v[33]), "+r"(v[34]), "+r"(v[35]), "+r"(v[36]), "+r"(v[37]), "+r"(v[38]), "+r"(v[39]),
+        "+r"(v[40]), "+r"(v[41]), "+r"(v[42]), "+r"(v[43]), "+r"(v[44]), "+r"(v[45]), "+r"(v[46]), "+r"(v[47]),
+        "+r"(v[48]), "+r"(v[49]), "+r"(v[50]), "+r"(v[51]), "+r"(v[52]), "+r"(v[53]), "+r"(v[54]), "+r"(v[55]),
+        "+r"(v[56]), "+r"(v[57]), "+r"(v[58]), "+r"(v[59]), "+r"(v[60]), "+r"(v[61]), "+r"(v[62]), "+r"(v[63])
+      :
+      : "memory");
+}
+
 __device__ __forceinline__ void epi_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiThreads) : "memory");
 }
 
-// acc.xy += p.xy * s.xy with one packed instruction.
-__device__ __forceinline__ void fma2(float2& acc, uint32_t p0, uint32_t p1, const float2& s) {
-  asm("{\n\t.reg .b64 pp, ss, aa;\n\t"
-      "mov.b64 pp, {%2, %3};\n\t"
-      "mov.b64 ss, {%4, %5};\n\t"
-      "mov.b64 aa, {%0, %1};\n\t"
-      "fma.rn.f32x2 aa, pp, ss, aa;\n\t"
-      "mov.b64 {%0, %1}, aa;\n\t}"
-      : "+f"(acc.x), "+f"(acc.y)
-      : "r"(p0), "r"(p1), "f"(s.x), "f"(s.y));
+// Two fp32 accumulators live in one 64-bit register: acc.{lo,hi} += p.{0,1} * s.{lo,hi} with one
+// packed instruction (half the issue slots of two scalar fmas; the pack of p0/p1 costs nothing when
+// they are adjacent registers, which the outputs of one tcgen05.ld are).
+__device__ __forceinline__ void fma2(unsigned long long& acc, uint32_t p0, uint32_t p1, unsigned long long s2) {
+  asm("{\n\t.reg .b64 pp;\n\t"
+      "mov.b64 pp, {%1, %2};\n\t"
+      "fma.rn.f32x2 %0, pp, %3, %0;\n\t}"
+      : "+l"(acc)
+      : "r"(p0), "r"(p1), "l"(s2));
+}
+
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+
+__device__ __forceinline__ float2 unpack2(unsigned long long v) {
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -219,22 +351,27 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   return d;
 }
 
-// kind::f8f6f4 instruction descriptor: D = fp32, A = B = e4m3, both K-major, M = 128, N = block_n.
-__host__ __device__ constexpr uint32_t make_idesc(int block_n) {
+// kind::f8f6f4 instruction descriptor: D = fp32, A = B = e4m3, both K-major, M x N as given.
+__host__ __device__ constexpr uint32_t make_idesc(int umma_m, int umma_n) {
   return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) |
-         (static_cast<uint32_t>(block_n >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+         (static_cast<uint32_t>(umma_n >> 3) << 17) | (static_cast<uint32_t>(umma_m >> 4) << 24);
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 struct TileCfg {
+  static constexpr int kTileM = PAIR ? 2 * kBlockM : kBlockM;  // rows of C per tile
+  static constexpr int kRowsB = PAIR ? BN / 2 : BN;            // rows of B this CTA loads per stage
   static constexpr int kStageBytesA = kBlockM * kBlockK;
-  static constexpr int kStageBytesB = BN * kBlockK;
+  static constexpr int kStageBytesB = kRowsB * kBlockK;
   static constexpr int kStageBytes = kStageBytesA + kStageBytesB;
   static constexpr int kTmemBufs = (BN <= 128) ? 4 : 2;
   static constexpr int kTmemColsUsed = kTmemBufs * BN;
   static constexpr int kTmemCols = kTmemColsUsed <= 256 ? 256 : 512;  // power of two >= 32
-  static constexpr int kColsPerThread = BN / 2;                        // two epilogue warpgroups
-  static constexpr int kChunks = kColsPerThread / 32;
+  static constexpr int kColsPerThread = BN / 2;                        // two promotion warpgroups
+  // Columns fetched from TMEM per tcgen05.ld: as wide as the registers allow (tcgen05.wait::ld
+  // waits for every outstanding fetch, so several narrow fetches in flight gain nothing).
+  static constexpr int kChunkCols = (kColsPerThread % 64 == 0) ? 64 : 32;
+  static constexpr int kChunks = kColsPerThread / kChunkCols;
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "block_n must be 64, 128, 192 or 256");
 };
 
@@ -242,7 +379,9 @@ struct WorkItem {
   int m0, n0, tile, split, kb_begin, kb_end;
 };
 
-__device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, int block_n) {
+// Work item w -> tile and K range. Tiles are walked in groups of raster_group tile rows, column
+// by column inside a group, so that the CTAs running at one time share A and B tiles in L2.
+__device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, int tile_m, int block_n) {
   WorkItem it;
   it.split = w % p.split_k;
   const int t = w / p.split_k;
@@ -254,7 +393,7 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
   const int within = t - group * per_group;
   const int tm = first_m + within % gsize;
   const int tn = within / gsize;
-  it.m0 = tm * kBlockM;
+  it.m0 = tm * tile_m;
   it.n0 = tn * block_n;
   it.kb_begin = static_cast<int>((static_cast<long long>(it.split) * p.kblocks) / p.split_k);
   it.kb_end = static_cast<int>((static_cast<long long>(it.split + 1) * p.kblocks) / p.split_k);
@@ -265,35 +404,44 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
 // The kernel
 // ---------------------------------------------------------------------------------------------
 
-template <int BN, int STAGES>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const KernelParams p) {
-  using Cfg = TileCfg<BN>;
+  using Cfg = TileCfg<BN, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   // SWIZZLE_128B tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes);
-  uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + STAGES;
-  uint64_t* tmem_full_bar = bars + 2 * STAGES;
-  uint64_t* tmem_empty_bar = bars + 2 * STAGES + Cfg::kTmemBufs;
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2 * Cfg::kTmemBufs);
+  const int stages = p.stages;
+  float* scale_ring = reinterpret_cast<float*>(smem + stages * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(scale_ring + kScaleSlots * kScaleSlotFloats);
+  uint64_t* full_bar = bars;                                 // [kMaxStages]
+  uint64_t* empty_bar = bars + kMaxStages;                   // [kMaxStages]
+  uint64_t* tmem_full_bar = bars + 2 * kMaxStages;           // [4]
+  uint64_t* tmem_empty_bar = bars + 2 * kMaxStages + 4;      // [4]
+  uint64_t* scale_full_bar = bars + 2 * kMaxStages + 8;      // [kScaleSlots]
+  uint64_t* scale_empty_bar = scale_full_bar + kScaleSlots;  // [kScaleSlots]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(scale_empty_bar + kScaleSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
 
   const int warp = static_cast<int>(threadIdx.x) >> 5;
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const AbortCtx ctx{abort_flag, p.status};
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), PAIR ? 2 : 1);  // one arrive.expect_tx per producing CTA
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    for (int b = 0; b < Cfg::kTmemBufs; ++b) {
+    for (int b = 0; b < 4; ++b) {
       mbar_init(smem_u32(&tmem_full_bar[b]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[b]), kNumEpiWarps);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), PAIR ? 2 * kNumEpiWarps : kNumEpiWarps);
+    }
+    for (int s = 0; s < kScaleSlots; ++s) {
+      mbar_init(smem_u32(&scale_full_bar[s]), 32);
+      mbar_init(smem_u32(&scale_empty_bar[s]), kNumEpiWarps);
     }
     *abort_flag = 0;
     *last_flag = 0;
@@ -302,86 +450,151 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
   }
   if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)),
-                 "r"(Cfg::kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(tmem_base_slot)),
+                   "r"(Cfg::kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(tmem_base_slot)),
+                   "r"(Cfg::kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers are initialised before any remote arrive
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
   const int total_work = p.tiles_m * p.tiles_n * p.split_k;
+  const int work_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int work_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const WorkItem it = decode_work(p, w, BN);
-        for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
-          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, ctx, 0x100 | stage)) {
-            ok = false;
-            break;
-          }
-          const uint32_t fb = smem_u32(&full_bar[stage]);
-          mbar_expect_tx(fb, Cfg::kStageBytes);
-          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
-          tma_load_2d(sa, &tmap_a, kb * kBlockK, it.m0, fb);
-          tma_load_2d(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, it.n0, fb);
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(BN == 256 ? kRegsLightWide : kRegsLight));
+    if (warp == 0) {
+      // ---------------- TMA producer ----------------
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int w = work_first; w < total_work && ok; w += work_step) {
+          const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+          const int a_row = it.m0 + static_cast<int>(cta_rank) * kBlockM;
+          const int b_row = it.n0 + static_cast<int>(cta_rank) * (PAIR ? Cfg::kRowsB : 0);
+          for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+            if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, ctx, 0x100 | stage)) {
+              ok = false;
+              break;
+            }
+            // Both CTAs of a pair report to the leader's barrier: its MMA thread consumes the stage.
+            const uint32_t fb = PAIR ? map_to_cta(smem_u32(&full_bar[stage]), 0) : smem_u32(&full_bar[stage]);
+            mbar_expect_tx_cluster(fb, Cfg::kStageBytes);
+            const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+            tma_load_2d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, fb);
+            tma_load_2d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, fb);
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BN);
-      int stage = 0, buf = 0;
-      uint32_t phase = 0, bphase = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-        const WorkItem it = decode_work(p, w, BN);
-        for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
-          if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), bphase ^ 1u, ctx, 0x200 | buf) ||
-              !mbar_wait(smem_u32(&full_bar[stage]), phase, ctx, 0x300 | stage)) {
-            ok = false;
-            break;
-          }
-          tcgen05_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
-          const uint64_t desc_a = make_smem_desc(sa);
-          const uint64_t desc_b = make_smem_desc(sa + Cfg::kStageBytesA);
-          const uint32_t d_addr = tmem_base + static_cast<uint32_t>(buf * BN);
+      __syncwarp();
+    } else if (warp == 1) {
+      // ---------------- MMA issuer (the leader CTA of a pair issues for both) ----------------
+      if (lane == 0 && cta_rank == 0) {
+        constexpr uint32_t idesc = make_idesc(Cfg::kTileM, BN);
+        int stage = 0, buf = 0;
+        uint32_t phase = 0, bphase = 0;
+        bool ok = true;
+        for (int w = work_first; w < total_work && ok; w += work_step) {
+          const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+          for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+            if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), bphase ^ 1u, ctx, 0x200 | buf) ||
+                !mbar_wait(smem_u32(&full_bar[stage]), phase, ctx, 0x300 | stage)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after();
+            const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+            const uint64_t desc_a = make_smem_desc(sa);
+            const uint64_t desc_b = make_smem_desc(sa + Cfg::kStageBytesA);
+            const uint32_t d_addr = tmem_base + static_cast<uint32_t>(buf * BN);
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            // 32 bytes further along K inside the 128-byte swizzle row = +2 in 16-byte units.
-            umma_f8(d_addr, desc_a + static_cast<uint64_t>(2 * k), desc_b + static_cast<uint64_t>(2 * k), idesc,
-                    k > 0 ? 1u : 0u);
-          }
-          umma_commit(smem_u32(&empty_bar[stage]));
-          umma_commit(smem_u32(&tmem_full_bar[buf]));
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
-          if (++buf == Cfg::kTmemBufs) {
-            buf = 0;
-            bphase ^= 1u;
+            for (int k = 0; k < kMmasPerBlock; ++k) {
+              // 32 bytes further along K inside the 128-byte swizzle row = +2 in 16-byte units.
+              umma_f8<PAIR>(d_addr, desc_a + static_cast<uint64_t>(2 * k), desc_b + static_cast<uint64_t>(2 * k),
+                            idesc, k > 0 ? 1u : 0u);
+            }
+            umma_commit<PAIR>(smem_u32(&empty_bar[stage]));
+            umma_commit<PAIR>(smem_u32(&tmem_full_bar[buf]));
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            if (++buf == Cfg::kTmemBufs) {
+              buf = 0;
+              bphase ^= 1u;
+            }
           }
         }
       }
+      __syncwarp();
+    } else if (warp == 3) {
+      // ---------------- scale loader ----------------
+      // One ring slot holds the scales of kScaleGroup consecutive K blocks of the current tile:
+      // a[row][u] for the CTA's 128 rows and b[j][u] for the (up to 4) b_scale rows the tile touches.
+      int slot = 0;
+      uint32_t sphase = 0;
+      bool ok = true;
+      for (int w = work_first; w < total_work && ok; w += work_step) {
+        const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+        const int row0 = it.m0 + static_cast<int>(cta_rank) * kBlockM;
+        const float* a_src[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          a_src[r] = p.a_scale + static_cast<long long>(min(row0 + lane + 32 * r, p.M - 1)) * p.sa_m;
+        // lanes 0..15: b_scale row (n0 + n_phase)/128 + lane/4 (clamped), K block offset lane%4
+        const int jb = min(((it.n0 + p.n_phase) >> 7) + ((lane >> 2) & 3), p.b_scale_rows - 1);
+        const float* b_src = p.b_scale + static_cast<long long>(jb) * p.sb_n;
+        for (int kb = it.kb_begin; kb < it.kb_end; kb += kScaleGroup) {
+          if (!mbar_wait(smem_u32(&scale_empty_bar[slot]), sphase ^ 1u, ctx, 0x500 | slot)) {
+            ok = false;
+            break;
+          }
+          const uint32_t dst = smem_u32(scale_ring + slot * kScaleSlotFloats);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+#pragma unroll
+            for (int u = 0; u < kScaleGroup; ++u) {
+              const int kk = min(kb + u, it.kb_end - 1);  // the tail of a K range repeats its last block
+              cp_async_4(dst + static_cast<uint32_t>(4 * ((lane + 32 * r) * kScaleGroup + u)),
+                         a_src[r] + static_cast<long long>(kk) * p.sa_k);
+            }
+          }
+          if (lane < 16) {
+            const int kk = min(kb + (lane & 3), it.kb_end - 1);
+            cp_async_4(dst + static_cast<uint32_t>(4 * (kBlockM * kScaleGroup + lane)),
+                       b_src + static_cast<long long>(kk) * p.sb_k);
+          }
+          cp_async_arrive_noinc(smem_u32(&scale_full_bar[slot]));
+          if (++slot == kScaleSlots) {
+            slot = 0;
+            sphase ^= 1u;
+          }
+        }
+      }
+      // Nothing may still be writing shared memory when the CTA exits.
+      asm volatile("cp.async.wait_all;" ::: "memory");
     }
-    __syncwarp();
-  } else if (warp >= 4) {
+  } else {
     // ---------------- promotion + store ----------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(BN == 256 ? kRegsHeavyWide : kRegsHeavy));
     const int ew = warp - 4;
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) belong to warps with this id mod 4
     const int half = ew >> 2;      // which half of the tile's columns
@@ -389,70 +602,100 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     const int col_base = half * Cfg::kColsPerThread;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int epi_tid = static_cast<int>(threadIdx.x) - 128;
+    // The MMA thread that waits for "buffer drained" lives in the leader CTA.
+    const uint32_t tmem_empty_base =
+        PAIR ? map_to_cta(smem_u32(&tmem_empty_bar[0]), 0) : smem_u32(&tmem_empty_bar[0]);
 
-    int buf = 0;
-    uint32_t bphase = 0;
+    int buf = 0, slot = 0;
+    uint32_t bphase = 0, sphase = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
-      const WorkItem it = decode_work(p, w, BN);
-      const int row = it.m0 + row_in_tile;
-      const int row_ld = min(row, p.M - 1);
-      const float* as_ptr = p.a_scale + static_cast<long long>(row_ld) * p.sa_m;
-      // b_scale rows this thread's columns can touch (at most 2 for <= 128 columns).
+
+    for (int w = work_first; w < total_work && ok; w += work_step) {
+      const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+      const int row = it.m0 + static_cast<int>(cta_rank) * kBlockM + row_in_tile;
+      // Index of this thread's first b_scale row inside a ring slot (at most 2 rows per 128 columns).
       const int gcol0 = it.n0 + col_base + p.n_phase;
       const int jb0 = gcol0 >> 7;
-      const int jb_lo = min(jb0, p.b_scale_rows - 1);
-      const int jb_hi = min(jb0 + 1, p.b_scale_rows - 1);
-      const float* bs_lo = p.b_scale + static_cast<long long>(jb_lo) * p.sb_n;
-      const float* bs_hi = p.b_scale + static_cast<long long>(jb_hi) * p.sb_n;
+      const int bi0 = jb0 - ((it.n0 + p.n_phase) >> 7);
 
-      float2 acc[Cfg::kColsPerThread / 2];
+      unsigned long long acc2[Cfg::kColsPerThread / 2];  // column pairs (2j, 2j+1)
 #pragma unroll
-      for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+      for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) acc2[j] = 0ull;
 
-      float a_s = __ldg(as_ptr + static_cast<long long>(it.kb_begin) * p.sa_k);
-      float b_lo = __ldg(bs_lo + static_cast<long long>(it.kb_begin) * p.sb_k);
-      float b_hi = __ldg(bs_hi + static_cast<long long>(it.kb_begin) * p.sb_k);
-
-      for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
-        const float s_lo = a_s * b_lo;
-        const float s_hi = a_s * b_hi;
-        if (kb + 1 < it.kb_end) {
-          a_s = __ldg(as_ptr + static_cast<long long>(kb + 1) * p.sa_k);
-          b_lo = __ldg(bs_lo + static_cast<long long>(kb + 1) * p.sb_k);
-          b_hi = __ldg(bs_hi + static_cast<long long>(kb + 1) * p.sb_k);
-        }
-        if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), bphase, ctx, 0x400 | buf)) {
+      for (int kb0 = it.kb_begin; kb0 < it.kb_end && ok; kb0 += kScaleGroup) {
+        // Scales of the next (up to) four K blocks: three 16-byte shared-memory loads, then the
+        // slot goes back to the loader.
+        if (!mbar_wait(smem_u32(&scale_full_bar[slot]), sphase, ctx, 0x600 | slot)) {
           ok = false;
           break;
         }
-        tcgen05_fence_after();
-        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(buf * BN + col_base);
-        uint32_t v[2][32];
-        tmem_ld_32x32(taddr, v[0]);
-#pragma unroll
-        for (int ch = 0; ch < Cfg::kChunks; ++ch) {
-          tmem_ld_wait(v[ch & 1]);
-          if (ch + 1 < Cfg::kChunks) {
-            tmem_ld_32x32(taddr + static_cast<uint32_t>((ch + 1) * 32), v[(ch + 1) & 1]);
-          } else {
-            // Every column of this buffer is in registers: hand it back to the MMA warp.
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
-          }
-          const float s = (((gcol0 + ch * 32) >> 7) == jb0) ? s_lo : s_hi;
-          const float2 s2 = make_float2(s, s);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) fma2(acc[ch * 16 + j], v[ch & 1][2 * j], v[ch & 1][2 * j + 1], s2);
+        const float4* sl = reinterpret_cast<const float4*>(scale_ring + slot * kScaleSlotFloats);
+        const float4 a4 = sl[row_in_tile];
+        const float4 blo4 = sl[kBlockM + bi0];
+        const float4 bhi4 = sl[kBlockM + bi0 + 1];
+        const float s_lo[kScaleGroup] = {a4.x * blo4.x, a4.y * blo4.y, a4.z * blo4.z, a4.w * blo4.w};
+        const float s_hi[kScaleGroup] = {a4.x * bhi4.x, a4.y * bhi4.y, a4.z * bhi4.z, a4.w * bhi4.w};
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&scale_empty_bar[slot]));
+        if (++slot == kScaleSlots) {
+          slot = 0;
+          sphase ^= 1u;
         }
-        if (++buf == Cfg::kTmemBufs) {
-          buf = 0;
-          bphase ^= 1u;
+
+#pragma unroll
+        for (int u = 0; u < kScaleGroup; ++u) {
+          if (kb0 + u >= it.kb_end) break;
+          if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), bphase, ctx, 0x400 | buf)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(buf * BN + col_base);
+          constexpr int CC = Cfg::kChunkCols;
+          uint32_t v[CC];
+          tmem_ld(taddr, v);
+#pragma unroll
+          for (int ch = 0; ch < Cfg::kChunks; ++ch) {
+            tmem_ld_wait(v);
+            if (ch + 1 == Cfg::kChunks) {
+              // Every column of this buffer is in registers (tcgen05.wait::ld has returned in every
+              // lane once __syncwarp is passed): hand it back to the MMA warp.
+              __syncwarp();
+              if (lane == 0) {
+                if constexpr (PAIR) {
+                  mbar_arrive_cluster(tmem_empty_base + static_cast<uint32_t>(buf * 8));
+                } else {
+                  mbar_arrive(tmem_empty_base + static_cast<uint32_t>(buf * 8));
+                }
+              }
+            }
+            const float s = (((gcol0 + ch * CC) >> 7) == jb0) ? s_lo[u] : s_hi[u];
+            const unsigned long long s2 = pack2(s, s);
+            if constexpr (CC <= 32) {
+#pragma unroll
+              for (int j = 0; j < CC / 2; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], s2);
+            } else {
+              // a 64-column fetch can straddle a scale-row boundary at its middle
+              const float sb = (((gcol0 + ch * CC + 32) >> 7) == jb0) ? s_lo[u] : s_hi[u];
+              const unsigned long long sb2 = pack2(sb, sb);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], s2);
+#pragma unroll
+              for (int j = 16; j < 32; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], sb2);
+            }
+            if (ch + 1 < Cfg::kChunks) tmem_ld(taddr + static_cast<uint32_t>((ch + 1) * CC), v);
+          }
+          if (++buf == Cfg::kTmemBufs) {
+            buf = 0;
+            bphase ^= 1u;
+          }
         }
       }
       if (!ok) break;
 
+      float2 acc[Cfg::kColsPerThread / 2];
+#pragma unroll
+      for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) acc[j] = unpack2(acc2[j]);
       const int col0 = it.n0 + col_base;  // first column of this thread inside (the shard of) c
       if (p.split_k == 1) {
         if (row < p.M) {
@@ -479,11 +722,12 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       } else {
         // Split-K: publish this K range's fp32 tile, then the last CTA to arrive for the tile
         // sums the ranges in order 0..split_k-1 (so the result does not depend on arrival order).
-        // Plane layout per (tile, split): float4 index (col/4)*128 + row, so that a warp's store
-        // covers 512 contiguous bytes.
+        // Plane layout per (tile, CTA of the pair, split): float4 index (col/4)*128 + row, so that
+        // a warp's store covers 512 contiguous bytes.
         const size_t plane_floats = static_cast<size_t>(kBlockM) * BN;
-        float4* mine = reinterpret_cast<float4*>(p.partials +
-                                                 (static_cast<size_t>(it.tile) * p.split_k + it.split) * plane_floats);
+        const size_t unit = static_cast<size_t>(it.tile) * (PAIR ? 2 : 1) + cta_rank;
+        float* unit_base = p.partials + unit * p.split_k * plane_floats;
+        float4* mine = reinterpret_cast<float4*>(unit_base + static_cast<size_t>(it.split) * plane_floats);
 #pragma unroll
         for (int j = 0; j < Cfg::kColsPerThread / 4; ++j) {
           const int c4 = (col_base >> 2) + j;
@@ -493,9 +737,9 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         __threadfence();
         epi_bar_sync();
         if (epi_tid == 0) {
-          const int prev = atomicAdd(p.counters + it.tile, 1);
+          const int prev = atomicAdd(p.counters + unit, 1);
           const int last = (prev == p.split_k - 1) ? 1 : 0;
-          if (last) p.counters[it.tile] = 0;  // leave the counters zero for the next launch
+          if (last) p.counters[unit] = 0;  // leave the counters zero for the next launch
           *last_flag = last;
         }
         epi_bar_sync();
@@ -503,8 +747,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         epi_bar_sync();  // everyone has read the flag before thread 0 can overwrite it
         if (is_last) {
           __threadfence();
-          const float4* base =
-              reinterpret_cast<const float4*>(p.partials + static_cast<size_t>(it.tile) * p.split_k * plane_floats);
+          const float4* base = reinterpret_cast<const float4*>(unit_base);
           if (row < p.M) {
             __nv_bfloat16* crow = p.c + static_cast<long long>(row) * p.ldc;
 #pragma unroll 2
@@ -537,13 +780,21 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     }
   }
 
-  // Teardown: every role has left its loop (normally or through an expired wait).
+  if (warp >= 4) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");  // none in flight past here
+  // Teardown: every role has left its loop (normally or through an expired wait). In a pair no
+  // CTA may exit while its peer can still signal its barriers or use its shared memory.
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();
   if (warp == 2) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols)
-                 : "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols)
+                   : "memory");
+    } else {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols)
+                   : "memory");
+    }
   }
 }
 
@@ -584,16 +835,17 @@ bool encode_operand_map(CUtensorMap* map, const void* base, int rows, int K, lon
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-int smem_bytes_for(int block_n, int stages) {
-  const int stage = kBlockM * kBlockK + block_n * kBlockK;
-  return stages * stage + 1024 /* alignment slack */ + 256 /* barriers and flags */;
+int smem_bytes_for(int block_n, int stages, int pair) {
+  const int stage = kBlockM * kBlockK + (pair ? block_n / 2 : block_n) * kBlockK;
+  return stages * stage + kScaleSlots * kScaleSlotFloats * 4 + 512 /* barriers and flags */ +
+         1024 /* alignment slack */;
 }
 
 constexpr int kMaxSmem = 232448;  // 227 KiB opt-in limit per CTA on sm_100
 
-int max_stages_for(int block_n) {
-  int s = 8;
-  while (s > 2 && smem_bytes_for(block_n, s) > kMaxSmem) --s;
+int max_stages_for(int block_n, int pair) {
+  int s = kMaxStages;
+  while (s > 2 && smem_bytes_for(block_n, s, pair) > kMaxSmem) --s;
   return s;
 }
 
@@ -601,14 +853,18 @@ bool valid_block_n(int bn) { return bn == 64 || bn == 128 || bn == 192 || bn == 
 
 size_t plan_workspace_bytes(const b200_fp8_mm_plan& pl) {
   if (pl.split_k <= 1) return 0;
-  return static_cast<size_t>(kCounterBytes) +
-         static_cast<size_t>(pl.tiles) * pl.split_k * kBlockM * pl.block_n * sizeof(float);
+  return static_cast<size_t>(kCounterBytes) + static_cast<size_t>(pl.tiles) * (pl.cta_pair ? 2 : 1) *
+                                                  pl.split_k * kBlockM * pl.block_n * sizeof(float);
 }
 
 // Tile/launch selection: a pure function of the problem and the SM count.
 void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forced, b200_fp8_mm_plan* out) {
   const int kblocks = K / kBlockK;
-  const int tiles_m = ceil_div(M, kBlockM);
+  int pair = 0;
+  if (forced && forced->cta_pair) pair = forced->cta_pair > 0 ? 1 : 0;  // -1 forces single CTAs
+  const int tile_m = pair ? 2 * kBlockM : kBlockM;
+  const int tiles_m = ceil_div(M, tile_m);
+  const int units = pair ? sm_count / 2 : sm_count;  // tiles that run at one time
   int bn = (forced && forced->block_n) ? forced->block_n : 0;
   int split = (forced && forced->split_k) ? forced->split_k : 0;
   if (bn == 0) {
@@ -618,7 +874,7 @@ void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forc
     for (int i = 0; i < 4; ++i) {
       const int c = cands[i];
       const int tiles = tiles_m * ceil_div(N, c);
-      const int waves = ceil_div(tiles, sm_count);
+      const int waves = ceil_div(tiles, units);
       // Cost model in MMA clocks per K block: time of a 128 x c block on the tensor pipe, floored by
       // the shared-memory operand traffic (128 B/clk) of a 128 x c x 32 instruction.
       const double mma = c / 64.0 * 128.0;
@@ -635,58 +891,45 @@ void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forc
   const int tiles = tiles_m * tiles_n;
   if (split == 0) {
     split = 1;
-    if (tiles * 2 <= sm_count && kblocks >= 8 && tiles <= kMaxCounters) {
-      split = sm_count / tiles;
+    if (tiles * 2 <= units && kblocks >= 8 && tiles * (pair ? 2 : 1) <= kMaxCounters) {
+      split = units / tiles;
       const int max_split = kblocks / 4;
       if (split > max_split) split = max_split;
       if (split > 16) split = 16;
       if (split < 1) split = 1;
     }
   }
-  int stages = (forced && forced->stages) ? forced->stages : max_stages_for(bn);
+  int stages = (forced && forced->stages) ? forced->stages : max_stages_for(bn, pair);
   out->block_m = kBlockM;
   out->block_n = bn;
-  out->cta_pair = 0;
+  out->cta_pair = pair;
   out->split_k = split;
   out->stages = stages;
   out->tiles = tiles;
   const int work = tiles * split;
-  out->grid = work < sm_count ? work : sm_count;
-  out->smem_bytes = smem_bytes_for(bn, stages);
+  const int used = work < units ? work : units;
+  out->grid = pair ? 2 * used : used;
+  out->smem_bytes = smem_bytes_for(bn, stages, pair);
 }
 
 bool plan_is_supported(const b200_fp8_mm_plan& pl, int kblocks) {
   if (!valid_block_n(pl.block_n)) return false;
-  if (pl.cta_pair != 0) return false;
-  if (pl.stages < 2 || pl.stages > 8) return false;
+  if (pl.cta_pair != 0 && pl.cta_pair != 1) return false;
+  if (pl.stages < 2 || pl.stages > kMaxStages) return false;
   if (pl.smem_bytes > kMaxSmem) return false;
   if (pl.split_k < 1 || pl.split_k > kblocks) return false;
-  if (pl.split_k > 1 && pl.tiles > kMaxCounters) return false;
+  if (pl.split_k > 1 && pl.tiles * (pl.cta_pair ? 2 : 1) > kMaxCounters) return false;
   return true;
 }
 
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const KernelParams);
 
-template <int BN>
-KernelFn kernel_for_stages(int stages) {
-  switch (stages) {
-    case 2: return fp8_mm_blockscaled_kernel<BN, 2>;
-    case 3: return fp8_mm_blockscaled_kernel<BN, 3>;
-    case 4: return fp8_mm_blockscaled_kernel<BN, 4>;
-    case 5: return fp8_mm_blockscaled_kernel<BN, 5>;
-    case 6: return fp8_mm_blockscaled_kernel<BN, 6>;
-    case 7: return fp8_mm_blockscaled_kernel<BN, 7>;
-    case 8: return fp8_mm_blockscaled_kernel<BN, 8>;
-    default: return nullptr;
-  }
-}
-
-KernelFn kernel_for(int block_n, int stages) {
+KernelFn kernel_for(int block_n, int pair) {
   switch (block_n) {
-    case 64: return kernel_for_stages<64>(stages);
-    case 128: return kernel_for_stages<128>(stages);
-    case 192: return kernel_for_stages<192>(stages);
-    case 256: return kernel_for_stages<256>(stages);
+    case 64: return pair ? fp8_mm_blockscaled_kernel<64, true> : fp8_mm_blockscaled_kernel<64, false>;
+    case 128: return pair ? fp8_mm_blockscaled_kernel<128, true> : fp8_mm_blockscaled_kernel<128, false>;
+    case 192: return pair ? fp8_mm_blockscaled_kernel<192, true> : fp8_mm_blockscaled_kernel<192, false>;
+    case 256: return pair ? fp8_mm_blockscaled_kernel<256, true> : fp8_mm_blockscaled_kernel<256, false>;
     default: return nullptr;
   }
 }
@@ -723,7 +966,6 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
 
   b200_fp8_mm_plan pl;
   choose_plan(M, N, K, sm_count, forced, &pl);
-  if (forced && forced->cta_pair) pl.cta_pair = forced->cta_pair;
   const int kblocks = K / kBlockK;
   if (!plan_is_supported(pl, kblocks)) return B200_FP8_MM_ERR_PLAN;
   const size_t need = plan_workspace_bytes(pl);
@@ -731,12 +973,13 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
                    (reinterpret_cast<uintptr_t>(workspace) % 256) != 0))
     return B200_FP8_MM_ERR_WORKSPACE;
 
-  KernelFn fn = kernel_for(pl.block_n, pl.stages);
+  KernelFn fn = kernel_for(pl.block_n, pl.cta_pair);
   if (fn == nullptr) return B200_FP8_MM_ERR_PLAN;
 
   CUtensorMap map_a, map_b;
   if (!encode_operand_map(&map_a, a, M, K, lda, kBlockM)) return B200_FP8_MM_ERR_DRIVER;
-  if (!encode_operand_map(&map_b, b, N, K, ldb, pl.block_n)) return B200_FP8_MM_ERR_DRIVER;
+  if (!encode_operand_map(&map_b, b, N, K, ldb, pl.cta_pair ? pl.block_n / 2 : pl.block_n))
+    return B200_FP8_MM_ERR_DRIVER;
 
   KernelParams kp;
   memset(&kp, 0, sizeof(kp));
@@ -755,11 +998,19 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   kp.N = N;
   kp.K = K;
   kp.n_phase = n_phase;
-  kp.tiles_m = ceil_div(M, kBlockM);
+  kp.tiles_m = ceil_div(M, pl.cta_pair ? 2 * kBlockM : kBlockM);
   kp.tiles_n = ceil_div(N, pl.block_n);
   kp.split_k = pl.split_k;
   kp.kblocks = kblocks;
-  kp.raster_group = 8;
+  kp.stages = pl.stages;
+  {
+    // Tile rows per raster group: the tiles running at one time form a block as square as possible.
+    const int units = pl.cta_pair ? sm_count / 2 : sm_count;
+    int g = (units + kp.tiles_n / 2) / kp.tiles_n;
+    if (g < 1) g = 1;
+    if (g > 16) g = 16;
+    kp.raster_group = g;
+  }
   kp.b_scale_rows = ceil_div(N + n_phase, 128);
   kp.vec_store =
       ((reinterpret_cast<uintptr_t>(c) % 16) == 0 && (ldc % 8) == 0 && (N % 8) == 0) ? 1 : 0;
@@ -776,6 +1027,15 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   cfg.blockDim = dim3(kNumThreads, 1, 1);
   cfg.dynamicSmemBytes = static_cast<size_t>(pl.smem_bytes);
   cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  if (pl.cta_pair) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
   err = cudaLaunchKernelEx(&cfg, fn, map_a, map_b, kp);
   if (err != cudaSuccess) {
     (void)cudaGetLastError();

@@ -30,14 +30,22 @@ class ShardSpec:
 
 
 def shard_spec(n: int, world: int, rank: int) -> ShardSpec:
+    """Columns of rank `rank` of `world`. Columns are dealt in units of 64 (32 when N is not a
+    multiple of 64) so that every shard starts on a boundary the kernel's n_phase can express;
+    when the units do not divide evenly the first ranks get one unit more (N=576 over 8 ranks:
+    128 columns on rank 0, 64 on the others)."""
     if world < 1 or not (0 <= rank < world):
         raise ValueError("bad rank/world")
-    if n % world != 0:
-        raise ValueError(f"N={n} does not divide over {world} ranks")
-    per = n // world
-    if per % 32 != 0:
-        raise ValueError("columns per rank must be a multiple of 32 (n_phase granularity)")
-    c0, c1 = rank * per, (rank + 1) * per
+    unit = 64 if n % 64 == 0 else 32
+    if n % unit != 0:
+        raise ValueError(f"N={n} is not a multiple of 32: shards could not start on an n_phase boundary")
+    units = n // unit
+    if units < world:
+        raise ValueError(f"N={n} has only {units} shardable units for {world} ranks")
+    base, extra = divmod(units, world)
+    u0 = rank * base + min(rank, extra)
+    u1 = u0 + base + (1 if rank < extra else 0)
+    c0, c1 = u0 * unit, u1 * unit
     return ShardSpec(rank, world, c0, c1, c0 % SCALE_BLOCK, c0 // SCALE_BLOCK, (c1 - 1) // SCALE_BLOCK + 1)
 
 

@@ -1,0 +1,256 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Tolerance is the contract's: |c - ref| <= 1e-3 + 2e-2 * |ref| on the bf16 output, inputs
+e4m3fn on both sides. Small and medium shapes are compared with the CPU oracle directly;
+the largest configurations are checked on sampled rows plus size-independent properties
+(exact linearity in power-of-two scales, shard/whole agreement, run-to-run determinism)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import amd_developer_challenge_2025_b200 as pkg
+from amd_developer_challenge_2025_b200.fp8_mm import Fp8MmError, Plan, check_device_status
+from oracle import fp8_mm_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 2e-2, 1e-3
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def run(a, b, a_s, b_s, c, **kw):
+    out = pkg.fp8_mm(a, b, a_s, b_s, c, **kw)
+    check_device_status(c.device)
+    return out
+
+
+def assert_close(c, ref, what=""):
+    ok, excess, max_err = oracle.check(c, ref, RTOL, ATOL)
+    assert ok, f"{what}: worst excess over tolerance {excess}, max abs err {max_err}"
+
+
+def cuda_inputs(m, n, k, seed):
+    return pkg.make_inputs(m, n, k, seed, device="cuda")
+
+
+# ------------------------------------------------------------------ golden fixtures
+
+
+@pytest.mark.parametrize("name", ["one_block", "ragged_n", "n576_like", "shard_phase64", "odd_m"])
+def test_golden_fixture(name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    m, n, k, seed, phase = (int(v) for v in z["meta"])
+    a = torch.from_numpy(z["a"]).view(torch.float8_e4m3fn).cuda()
+    b = torch.from_numpy(z["b"]).view(torch.float8_e4m3fn).cuda()
+    a_s = torch.from_numpy(z["a_scale"]).cuda()
+    b_s = torch.from_numpy(z["b_scale"]).cuda()
+    want = torch.from_numpy(z["c_bf16_bits"]).view(torch.bfloat16)
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    run(a, b, a_s, b_s, c, n_phase=phase)
+    assert_close(c, want, name)
+
+
+# ------------------------------------------------------------------ the named configurations
+
+
+@pytest.mark.parametrize("m,n,k,seed", [
+    (256, 1536, 7168, 8135),   # the CPU-runnable configuration
+    (2048, 576, 7168, 12346),  # skinny N, long K (5 scale rows for 4.5 blocks)
+    (2048, 7168, 512, 17512),  # short K
+    (2048, 7168, 256, 5364),   # two scale blocks only
+])
+def test_named_config_against_cpu_oracle(m, n, k, seed):
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, seed)
+    c.fill_(float("nan"))
+    out = pkg.custom_kernel((a, b, a_s, b_s, c))
+    check_device_status()
+    assert out is c
+    assert_close(c, oracle.dequant_matmul(a, b, a_s, b_s), f"{m}x{n}x{k}")
+
+
+def test_headline_config_rows_and_properties():
+    """M=8192, N=4608, K=7168: sampled rows against the oracle, exact linearity, determinism."""
+    m, n, k = 8192, 4608, 7168
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, 65436)
+    run(a, b, a_s, b_s, c)
+    rows = torch.tensor(sorted({0, 1, 127, 128, 129, 255, 256, 4095, 4096, 8190, 8191} |
+                               set(torch.randint(0, m, (21,), generator=torch.Generator().manual_seed(1)).tolist())))
+    ref = oracle.dequant_matmul(a[rows.cuda()], b, a_s[rows.cuda()], b_s)
+    assert_close(c[rows.cuda()], ref, "sampled rows")
+    # doubling a_scale doubles every output bit-exactly (power-of-two scaling commutes with rounding)
+    c2 = torch.empty_like(c)
+    run(a, b, a_s * 2, b_s, c2)
+    assert torch.equal(c2.float(), c.float() * 2)
+    # same inputs, same plan -> same bits
+    c3 = torch.empty_like(c)
+    run(a, b, a_s, b_s, c3)
+    assert torch.equal(c3.view(torch.int16), c.view(torch.int16))
+    # every output was written exactly where it belongs: no NaN sentinel survives
+    c4 = torch.full_like(c, float("nan"))
+    run(a, b, a_s, b_s, c4)
+    assert torch.isfinite(c4.float()).all()
+
+
+# ------------------------------------------------------------------ edge cases
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (1, 64, 128), (7, 8, 128), (128, 128, 128), (129, 130, 256), (200, 576, 1024), (1000, 520, 384),
+    (128, 72, 256), (300, 1, 128), (257, 4099, 128), (512, 512, 7168), (4096, 512, 512),
+])
+def test_ragged_and_small_shapes(m, n, k):
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, m * 7 + n * 3 + k)
+    c.fill_(float("nan"))
+    run(a, b, a_s, b_s, c)
+    assert_close(c, oracle.dequant_matmul(a, b, a_s, b_s), f"{m}x{n}x{k}")
+
+
+PLANS = [Plan(block_n=bn, cta_pair=pr, split_k=sk)
+         for bn in (64, 128, 192, 256) for pr in (-1, 1) for sk in (1, 3)]
+
+
+@pytest.mark.parametrize("plan", PLANS, ids=lambda p: f"bn{p.block_n}_pair{p.cta_pair}_split{p.split_k}")
+def test_every_kernel_variant(plan):
+    m, n, k = 600, 1096, 1536
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, 99)
+    ref = oracle.dequant_matmul(a, b, a_s, b_s)
+    c.fill_(float("nan"))
+    run(a, b, a_s, b_s, c, plan=plan)
+    assert_close(c, ref, str(plan))
+    # and with a 2-deep ring, the shallowest pipeline
+    c.fill_(float("nan"))
+    run(a, b, a_s, b_s, c, plan=Plan(block_n=plan.block_n, cta_pair=plan.cta_pair, split_k=plan.split_k, stages=2))
+    assert_close(c, ref, str(plan) + " stages=2")
+
+
+def test_split_k_is_deterministic_and_leaves_counters_clean():
+    m, n, k = 256, 1536, 7168
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, 5)
+    plan = Plan(block_n=128, cta_pair=-1, split_k=4)
+    outs = []
+    for _ in range(3):
+        c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        run(a, b, a_s, b_s, c, plan=plan)
+        outs.append(c)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert torch.equal(outs[0].view(torch.int16), outs[2].view(torch.int16))
+    assert_close(outs[0], oracle.dequant_matmul(a, b, a_s, b_s))
+
+
+@pytest.mark.parametrize("phase", [0, 32, 64, 96])
+def test_column_shard_with_phase(phase):
+    """A shard that starts `phase` columns into a scale block equals those columns of the whole."""
+    m, k, n_full = 192, 512, 832
+    a, b, a_s, b_s, _ = cuda_inputs(m, n_full, k, 31)
+    whole = oracle.dequant_matmul(a, b, a_s, b_s)
+    c0 = 128 + phase
+    bb = b[c0:c0 + 576].contiguous()
+    bs = b_s[c0 // 128:(c0 + 576 - 1) // 128 + 1].contiguous()
+    c = torch.full((m, 576), float("nan"), dtype=torch.bfloat16, device="cuda")
+    run(a, bb, a_s, bs, c, n_phase=phase)
+    assert_close(c, whole[:, c0:c0 + 576], f"phase {phase}")
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_equals_whole_at_4608(world):
+    m, n, k = 512, 4608, 1024
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, 77)
+    run(a, b, a_s, b_s, c)
+    parts = []
+    for r in range(world):
+        spec = pkg.shard_spec(n, world, r)
+        bb, bs = pkg.shard_inputs(b, b_s, spec)
+        cc = torch.empty(m, spec.n_local, dtype=torch.bfloat16, device="cuda")
+        run(a, bb.contiguous(), a_s, bs.contiguous(), cc, n_phase=spec.n_phase)
+        parts.append(cc)
+    got = torch.cat(parts, dim=1)
+    assert_close(got, oracle.dequant_matmul(a, b, a_s, b_s), f"world {world}")
+    assert_close(got, c.cpu(), "sharded vs whole")
+
+
+def test_strided_operands_and_output():
+    """Row-padded a/b, M-major (transposed-storage) scales, and c as a column slice of a wider buffer."""
+    m, n, k = 300, 576, 768
+    a, b, a_s, b_s, _ = cuda_inputs(m, n, k, 8)
+    ref = oracle.dequant_matmul(a, b, a_s, b_s)
+    a_pad = torch.zeros(m, k + 64, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    a_pad[:, :k] = a
+    b_pad = torch.zeros(n, k + 128, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    b_pad[:, :k] = b
+    a_s_t = a_s.t().contiguous().t()  # element (i,kb) at kb*M + i: the reference harness's native layout
+    b_s_t = b_s.t().contiguous().t()
+    assert a_s_t.stride() == (1, m)
+    wide = torch.full((m, n + 40), float("nan"), dtype=torch.bfloat16, device="cuda")
+    c_view = wide[:, 8:8 + n]
+    run(a_pad[:, :k], b_pad[:, :k], a_s_t, b_s_t, c_view)
+    assert_close(c_view, ref, "strided")
+    assert torch.isnan(wide[:, :8].float()).all() and torch.isnan(wide[:, 8 + n:].float()).all()
+
+
+def test_inputs_are_not_modified_and_c_is_returned():
+    m, n, k = 384, 640, 512
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, 4)
+    keep = [t.clone() for t in (a.view(torch.uint8), b.view(torch.uint8), a_s, b_s)]
+    out = pkg.custom_kernel((a, b, a_s, b_s, c))
+    check_device_status()
+    assert out is c
+    for before, after in zip(keep, (a.view(torch.uint8), b.view(torch.uint8), a_s, b_s)):
+        assert torch.equal(before, after)
+
+
+def test_extreme_values_and_zero_scales():
+    """Largest finite e4m3fn magnitudes (+-448), zeros, subnormals; a zero scale zeroes its block."""
+    m, n, k = 128, 256, 256
+    g = torch.Generator().manual_seed(3)
+    codes = torch.tensor([0x7E, 0xFE, 0x00, 0x80, 0x01, 0x81, 0x08, 0x38], dtype=torch.uint8)
+    a = codes[torch.randint(0, 8, (m, k), generator=g)].view(torch.float8_e4m3fn).cuda()
+    b = codes[torch.randint(0, 8, (n, k), generator=g)].view(torch.float8_e4m3fn).cuda()
+    a_s = torch.rand(m, 2, generator=g).cuda()
+    b_s = torch.rand(2, 2, generator=g).cuda()
+    b_s[1, 0] = 0.0
+    c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    run(a, b, a_s, b_s, c)
+    assert_close(c, oracle.dequant_matmul(a, b, a_s, b_s), "extremes")
+
+
+def test_host_errors_raise_before_launch():
+    a, b, a_s, b_s, c = cuda_inputs(128, 128, 256, 1)
+    with pytest.raises(ValueError):
+        pkg.fp8_mm(a[:, :200], b[:, :200], a_s, b_s, c)            # K not a multiple of 128
+    with pytest.raises(ValueError):
+        pkg.fp8_mm(a, b, a_s[:, :1], b_s, c)                        # wrong a_scale shape
+    with pytest.raises(ValueError):
+        pkg.fp8_mm(a.view(torch.uint8), b, a_s, b_s, c)             # wrong dtype
+    with pytest.raises(ValueError):
+        pkg.fp8_mm(a.t().contiguous().t(), b, a_s, b_s, c)          # M-major a is rejected, not mis-read
+    with pytest.raises(Fp8MmError):
+        pkg.fp8_mm(a, b, a_s, b_s, c, plan=Plan(block_n=96))        # unsupported forced plan
+    with pytest.raises(Fp8MmError):
+        pkg.fp8_mm(a, b, a_s, b_s, c, n_phase=16)                   # phase granularity is 32
+    check_device_status()
+
+
+def test_host_buffer_entry_point():
+    m, n, k = 256, 576, 512
+    a, b, a_s, b_s, c = pkg.make_inputs(m, n, k, 12)
+    out = pkg.fp8_mm_host(a, b, a_s, b_s, c)
+    assert out is c and not c.is_cuda
+    assert_close(c, oracle.dequant_matmul(a, b, a_s, b_s), "host entry")
+
+
+def test_non_default_stream_and_back_to_back_launches():
+    m, n, k = 512, 1024, 1024
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, 6)
+    ref = oracle.dequant_matmul(a, b, a_s, b_s)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    outs = [torch.empty_like(c) for _ in range(8)]
+    with torch.cuda.stream(s):
+        for o in outs:
+            pkg.fp8_mm(a, b, a_s, b_s, o)
+    s.synchronize()
+    check_device_status()
+    for o in outs:
+        assert_close(o, ref, "stream")

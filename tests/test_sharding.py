@@ -26,16 +26,25 @@ def test_spec_4608_over_8_ranks():
 
 def test_spec_rejects_bad_splits():
     with pytest.raises(ValueError):
-        shard_spec(100, 8, 0)
+        shard_spec(100, 8, 0)      # not a multiple of 32
     with pytest.raises(ValueError):
-        shard_spec(4608, 8, 8)
+        shard_spec(4608, 8, 8)     # rank out of range
     with pytest.raises(ValueError):
-        shard_spec(48 * 3, 3, 0)  # 48 columns per rank: not a multiple of 32
+        shard_spec(128, 4, 0)      # two 64-column units cannot feed four ranks
+
+
+def test_uneven_units_576_over_8():
+    specs = [shard_spec(576, 8, r) for r in range(8)]
+    assert [s.n_local for s in specs] == [128] + [64] * 7
+    assert specs[0].col_begin == 0 and specs[-1].col_end == 576
+    for a, b in zip(specs, specs[1:]):
+        assert a.col_end == b.col_begin
+    assert all(s.n_phase in (0, 64) for s in specs)
 
 
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_shards_tile_the_columns_and_reproduce_the_full_result(world):
-    m, n, k = 16, 576 * 4, 256
+    m, n, k = 16, 576, 256
     a, b, a_s, b_s, _ = make_inputs(m, n, k, seed=21)
     full = oracle.dequant_matmul(a, b, a_s, b_s)
     cols = []
@@ -79,7 +88,7 @@ def test_two_gloo_ranks_gather_equals_unsharded():
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, 8, 576, 256, out)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, 8, 1152, 256, out)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
