@@ -60,6 +60,8 @@ typedef struct b200_fp8_mm_plan {
   int grid;       /* CTAs launched (persistent; a multiple of 2 when cta_pair)      */
   int tiles;      /* output tiles (x split_k = work items)                          */
   int smem_bytes; /* dynamic shared memory per CTA                                  */
+  int store_bufs; /* staging buffers per warpgroup for the TMA store of c: 1 or 2;
+                     0 = plain stores (split-K plans, or forced with -1)             */
 } b200_fp8_mm_plan;
 
 /*
@@ -96,9 +98,10 @@ int b200_fp8_mm(const void* a, const void* b, const float* a_scale, const float*
                 void* workspace, size_t workspace_bytes,
                 int* device_status, void* stream);
 
-/* Same, with the plan given by the caller (block_n, cta_pair, split_k, stages
- * are read; 0 in any of them means "choose"). Used for sweeps and by the tests
- * to force every kernel variant. */
+/* Same, with the plan given by the caller (block_n, cta_pair, split_k, stages,
+ * store_bufs are read; 0 in any of them means "choose"; cta_pair -1 forces single
+ * CTAs, store_bufs -1 forces plain stores). Used for sweeps and by the tests to
+ * force every kernel variant. */
 int b200_fp8_mm_planned(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c,
                         int M, int N, int K,
                         long long lda, long long ldb,

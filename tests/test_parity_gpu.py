@@ -107,11 +107,14 @@ def test_ragged_and_small_shapes(m, n, k):
     assert_close(c, oracle.dequant_matmul(a, b, a_s, b_s), f"{m}x{n}x{k}")
 
 
-PLANS = [Plan(block_n=bn, cta_pair=pr, split_k=sk)
-         for bn in (64, 128, 192, 256) for pr in (-1, 1) for sk in (1, 3)]
+# every tile width x single CTA / CTA pair x {no split, split-K 3}; without a split also every way
+# the bf16 tile can leave: plain stores (-1), TMA store with 1 or 2 staging buffers
+PLANS = [Plan(block_n=bn, cta_pair=pr, split_k=sk, store_bufs=sb)
+         for bn in (64, 128, 192, 256) for pr in (-1, 1) for (sk, sb) in ((1, -1), (1, 1), (1, 2), (3, 0))]
 
 
-@pytest.mark.parametrize("plan", PLANS, ids=lambda p: f"bn{p.block_n}_pair{p.cta_pair}_split{p.split_k}")
+@pytest.mark.parametrize(
+    "plan", PLANS, ids=lambda p: f"bn{p.block_n}_pair{p.cta_pair}_split{p.split_k}_store{p.store_bufs}")
 def test_every_kernel_variant(plan):
     m, n, k = 600, 1096, 1536
     a, b, a_s, b_s, c = cuda_inputs(m, n, k, 99)
@@ -121,7 +124,8 @@ def test_every_kernel_variant(plan):
     assert_close(c, ref, str(plan))
     # and with a 2-deep ring, the shallowest pipeline
     c.fill_(float("nan"))
-    run(a, b, a_s, b_s, c, plan=Plan(block_n=plan.block_n, cta_pair=plan.cta_pair, split_k=plan.split_k, stages=2))
+    run(a, b, a_s, b_s, c, plan=Plan(block_n=plan.block_n, cta_pair=plan.cta_pair, split_k=plan.split_k,
+                                     store_bufs=plan.store_bufs, stages=2))
     assert_close(c, ref, str(plan) + " stages=2")
 
 
@@ -182,11 +186,14 @@ def test_strided_operands_and_output():
     a_s_t = a_s.t().contiguous().t()  # element (i,kb) at kb*M + i: the reference harness's native layout
     b_s_t = b_s.t().contiguous().t()
     assert a_s_t.stride() == (1, m)
-    wide = torch.full((m, n + 40), float("nan"), dtype=torch.bfloat16, device="cuda")
-    c_view = wide[:, 8:8 + n]
-    run(a_pad[:, :k], b_pad[:, :k], a_s_t, b_s_t, c_view)
-    assert_close(c_view, ref, "strided")
-    assert torch.isnan(wide[:, :8].float()).all() and torch.isnan(wide[:, 8 + n:].float()).all()
+    # c as a column slice of a wider buffer: offset 8 keeps the 16-byte alignment the TMA store needs,
+    # offset 3 does not and exercises the plain-store fallback
+    for off in (8, 3):
+        wide = torch.full((m, n + 40), float("nan"), dtype=torch.bfloat16, device="cuda")
+        c_view = wide[:, off:off + n]
+        run(a_pad[:, :k], b_pad[:, :k], a_s_t, b_s_t, c_view)
+        assert_close(c_view, ref, f"strided, column offset {off}")
+        assert torch.isnan(wide[:, :off].float()).all() and torch.isnan(wide[:, off + n:].float()).all()
 
 
 def test_inputs_are_not_modified_and_c_is_returned():
