@@ -12,10 +12,12 @@
 //   warp 0      TMA producer: A (128 x 128 B) and B tiles of one K block into a SWIZZLE_128B
 //               shared-memory ring, completion on an mbarrier per stage
 //   warp 1      MMA issuer: 4 x tcgen05.mma.kind::f8f6f4 (K=32 each) per K block into one of
-//               the TMEM partial buffers, tcgen05.commit to free the stage and publish the buffer.
-//               It waits on ONE barrier per K block: a stage's "full" barrier also collects the
-//               promotion warps' release of the TMEM buffer that K block will overwrite (stage s
-//               always pairs with buffer s mod kTmemBufs because the ring depth is a multiple of it)
+//               the TMEM partial buffers, then ONE tcgen05.commit to the stage's "done" barrier,
+//               which both frees the stage for the producer and publishes the buffer to the
+//               promotion warps. It waits on ONE barrier per K block: a stage's "full" barrier also
+//               collects the promotion warps' release of the TMEM buffer that K block will
+//               overwrite (stage s always pairs with buffer s mod buffers: the ring depth is a
+//               multiple of the buffer count)
 //   warp 2      allocates / frees TMEM
 //   warp 3      scale loader: cp.async of the a_scale / b_scale values of FOUR K blocks at a time
 //               into a small shared-memory ring, up to 16 K blocks ahead
@@ -236,22 +238,28 @@ __device__ __forceinline__ void tcgen05_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// Descriptors are passed as their 32-bit halves: only the low word (start address) changes from one
+// instruction to the next, which keeps the issuing thread's arithmetic to one add per operand.
 template <bool PAIR>
-__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                        uint32_t accumulate) {
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                        uint32_t idesc, uint32_t accumulate) {
   if constexpr (PAIR) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   } else {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   }
 }
@@ -365,17 +373,13 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-// K-major, SWIZZLE_128B shared-memory matrix descriptor (sm_100 format): start address and
-// stride-dimension offset in 16-byte units, 8-row groups 1024 bytes apart, version 1, layout 2.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
+// K-major, SWIZZLE_128B shared-memory matrix descriptor (sm_100 format), as two 32-bit words.
+// Low word: start address in 16-byte units (bits 0-13) and the (ignored) leading offset 1 (bit 16).
+// High word: 8-row groups 1024 bytes apart (stride offset 64 in 16-byte units), version 1, layout 2.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) {
+  return ((smem_addr >> 4) & 0x3fffu) | (1u << 16);
 }
+constexpr uint32_t kSmemDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
 
 // kind::f8f6f4 instruction descriptor: D = fp32, A = B = e4m3, both K-major, M x N as given.
 __host__ __device__ constexpr uint32_t make_idesc(int umma_m, int umma_n) {
@@ -445,8 +449,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   float* scale_ring = reinterpret_cast<float*>(smem + stages * Cfg::kStageBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(scale_ring + kScaleSlots * kScaleSlotFloats);
   uint64_t* full_bar = bars;                                 // [kMaxStages]
-  uint64_t* empty_bar = bars + kMaxStages;                   // [kMaxStages]
-  uint64_t* tmem_full_bar = bars + 2 * kMaxStages;           // [4]
+  uint64_t* done_bar = bars + kMaxStages;                    // [kMaxStages]
   uint64_t* scale_full_bar = bars + 2 * kMaxStages + 8;      // [kScaleSlots]
   uint64_t* scale_empty_bar = scale_full_bar + kScaleSlots;  // [kScaleSlots]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(scale_empty_bar + kScaleSlots);
@@ -465,10 +468,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     for (int s = 0; s < kMaxStages; ++s) {
       // one arrive.expect_tx per producing CTA + one release per promotion warp (of both CTAs)
       mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1) * (1 + kNumEpiWarps));
-      mbar_init(smem_u32(&empty_bar[s]), 1);
-    }
-    for (int b = 0; b < 4; ++b) {
-      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&done_bar[s]), 1);  // the MMA thread's commit
     }
     for (int s = 0; s < kScaleSlots; ++s) {
       mbar_init(smem_u32(&scale_full_bar[s]), 32);
@@ -519,7 +519,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           const int a_row = it.m0 + static_cast<int>(cta_rank) * kBlockM;
           const int b_row = it.n0 + static_cast<int>(cta_rank) * (PAIR ? Cfg::kRowsB : 0);
           for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
-            if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, ctx, 0x100 | stage)) {
+            if (!mbar_wait(smem_u32(&done_bar[stage]), phase ^ 1u, ctx, 0x100 | stage)) {
               ok = false;
               break;
             }
@@ -547,24 +547,22 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         for (int w = work_first; w < total_work && ok; w += work_step) {
           const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
           for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
+            const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+            const uint32_t a_lo = smem_desc_lo(sa);
+            const uint32_t b_lo = smem_desc_lo(sa + Cfg::kStageBytesA);
+            const uint32_t d_addr = tmem_base + static_cast<uint32_t>(buf * BN);
             // operands landed AND the TMEM buffer of this K block drained (see the promotion warps)
             if (!mbar_wait(smem_u32(&full_bar[stage]), phase, ctx, 0x300 | stage)) {
               ok = false;
               break;
             }
             tcgen05_fence_after();
-            const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
-            const uint64_t desc_a = make_smem_desc(sa);
-            const uint64_t desc_b = make_smem_desc(sa + Cfg::kStageBytesA);
-            const uint32_t d_addr = tmem_base + static_cast<uint32_t>(buf * BN);
 #pragma unroll
             for (int k = 0; k < kMmasPerBlock; ++k) {
-              // 32 bytes further along K inside the 128-byte swizzle row = +2 in 16-byte units.
-              umma_f8<PAIR>(d_addr, desc_a + static_cast<uint64_t>(2 * k), desc_b + static_cast<uint64_t>(2 * k),
-                            idesc, k > 0 ? 1u : 0u);
+              // 32 bytes further along K inside the 128-byte swizzle row = +2 in 16-byte units
+              umma_f8<PAIR>(d_addr, a_lo + 2u * k, b_lo + 2u * k, kSmemDescHi, idesc, k > 0 ? 1u : 0u);
             }
-            umma_commit<PAIR>(smem_u32(&empty_bar[stage]));
-            umma_commit<PAIR>(smem_u32(&tmem_full_bar[buf]));
+            umma_commit<PAIR>(smem_u32(&done_bar[stage]));
             if (++stage == stages) {
               stage = 0;
               phase ^= 1u;
@@ -648,8 +646,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     for (int b = 0; b < nbufs; ++b) release_to(b);
     int rel_stage = nbufs % stages;
 
-    int buf = 0, slot = 0;
-    uint32_t bphase = 0, sphase = 0;
+    int buf = 0, slot = 0, cstage = 0;
+    uint32_t cphase = 0, sphase = 0;
     bool ok = true;
 
     for (int w = work_first; w < total_work && ok; w += work_step) {
@@ -687,7 +685,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
         for (int u = 0; u < kScaleGroup; ++u) {
           if (kb0 + u >= it.kb_end) break;
-          if (!mbar_wait(smem_u32(&tmem_full_bar[buf]), bphase, ctx, 0x400 | buf)) {
+          if (!mbar_wait(smem_u32(&done_bar[cstage]), cphase, ctx, 0x400 | cstage)) {
             ok = false;
             break;
           }
@@ -722,9 +720,10 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             }
             if (ch + 1 < Cfg::kChunks) tmem_ld(taddr + static_cast<uint32_t>((ch + 1) * CC), v);
           }
-          if (++buf == nbufs) {
-            buf = 0;
-            bphase ^= 1u;
+          if (++buf == nbufs) buf = 0;
+          if (++cstage == stages) {
+            cstage = 0;
+            cphase ^= 1u;
           }
         }
       }
@@ -1171,11 +1170,22 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   kp.vec_store =
       ((reinterpret_cast<uintptr_t>(c) % 16) == 0 && (ldc % 8) == 0 && (N % 8) == 0) ? 1 : 0;
 
-  cudaError_t err = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn),
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
-  if (err != cudaSuccess) {
-    (void)cudaGetLastError();
-    return B200_FP8_MM_ERR_LAUNCH;
+  // Opt every kernel in to the full 227 KiB of dynamic shared memory once per device.
+  cudaError_t err = cudaSuccess;
+  {
+    static unsigned char opted_in[64][8] = {};
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    const int slot = (pl.block_n / 64 - 1) * 2 + (pl.cta_pair ? 1 : 0);
+    if (dev < 0 || dev >= 64 || !opted_in[dev][slot]) {
+      err = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kMaxSmem);
+      if (err != cudaSuccess) {
+        (void)cudaGetLastError();
+        return B200_FP8_MM_ERR_LAUNCH;
+      }
+      if (dev >= 0 && dev < 64) opted_in[dev][slot] = 1;
+    }
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));

@@ -95,15 +95,13 @@ def _check(cond: bool, msg: str):
         raise ValueError(msg)
 
 
-def fp8_mm(a, b, a_scale, b_scale, c, n_phase: int = 0, plan: Plan | None = None, check: bool = False):
-    """c[M,N] (bf16) = block-scaled a[M,K] @ b[N,K]^T on the current CUDA stream; returns c.
+# Argument signatures that already passed validation -> (workspace bytes, C plan or None). A repeat
+# call with the same shapes, strides, dtypes and device skips the checks: the operator is called in
+# tight loops and the kernel for a small problem runs for only a few microseconds.
+_validated: dict[tuple, tuple] = {}
 
-    a, b: float8_e4m3fn with K contiguous. a_scale: fp32 [M, K/128], any strides.
-    b_scale: fp32 [ceil((N+n_phase)/128), K/128], any strides. `n_phase`: offset of b's first
-    row inside its 128-row scale block (0 unless b is a column shard of a larger matrix).
-    `plan`: force tile parameters (sweeps/tests). `check`: synchronise and raise if a wait
-    inside the kernel expired. Asynchronous otherwise, like the reference's launcher."""
-    lib = _lib.load()
+
+def _validate(a, b, a_scale, b_scale, c, n_phase, plan):
     _check(a.is_cuda and b.is_cuda and a_scale.is_cuda and b_scale.is_cuda and c.is_cuda,
            "all five tensors must be CUDA tensors (there is no CPU path)")
     _check(a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn, "a and b must be float8_e4m3fn")
@@ -124,27 +122,49 @@ def fp8_mm(a, b, a_scale, b_scale, c, n_phase: int = 0, plan: Plan | None = None
     _check(c.stride(1) == 1, "c must have N contiguous")
     dev = a.device
     _check(all(t.device == dev for t in (b, a_scale, b_scale, c)), "tensors on different devices")
+    return workspace_bytes(m, n, k, plan), (plan.to_c() if plan is not None else None)
 
-    nbytes = workspace_bytes(m, n, k, plan)
+
+def fp8_mm(a, b, a_scale, b_scale, c, n_phase: int = 0, plan: Plan | None = None, check: bool = False):
+    """c[M,N] (bf16) = block-scaled a[M,K] @ b[N,K]^T on the current CUDA stream; returns c.
+
+    a, b: float8_e4m3fn with K contiguous. a_scale: fp32 [M, K/128], any strides.
+    b_scale: fp32 [ceil((N+n_phase)/128), K/128], any strides. `n_phase`: offset of b's first
+    row inside its 128-row scale block (0 unless b is a column shard of a larger matrix).
+    `plan`: force tile parameters (sweeps/tests). `check`: synchronise and raise if a wait
+    inside the kernel expired. Asynchronous otherwise, like the reference's launcher."""
+    lib = _lib.load()
+    sa, sb, sas, sbs, sc = a.stride(), b.stride(), a_scale.stride(), b_scale.stride(), c.stride()
+    key = (a.shape, b.shape, a_scale.shape, b_scale.shape, c.shape, sa, sb, sas, sbs, sc,
+           a.dtype, b.dtype, a_scale.dtype, b_scale.dtype, c.dtype,
+           a.device, b.device, a_scale.device, b_scale.device, c.device, n_phase, plan)
+    cached = _validated.get(key)
+    if cached is None:
+        cached = _validate(a, b, a_scale, b_scale, c, n_phase, plan)
+        if len(_validated) > 4096:
+            _validated.clear()
+        _validated[key] = cached
+    nbytes, cplan = cached
+    m, k = a.shape
+    n = b.shape[0]
+    dev = a.device
     ws = _workspace(dev, nbytes)
     st = _status_words(dev)
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        args = [
-            a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), c.data_ptr(),
-            m, n, k,
-            a.stride(0), b.stride(0),
-            a_scale.stride(0), a_scale.stride(1),
-            b_scale.stride(0), b_scale.stride(1),
-            c.stride(0), n_phase,
-            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-            st.data_ptr(), stream,
-        ]
-        if plan is None:
-            rc = lib.b200_fp8_mm(*args)
-        else:
-            cp = plan.to_c()
-            rc = lib.b200_fp8_mm_planned(*args, ctypes.byref(cp))
+    if dev.index != torch.cuda.current_device():
+        with torch.cuda.device(dev):
+            return fp8_mm(a, b, a_scale, b_scale, c, n_phase, plan, check)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    args = (
+        a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), c.data_ptr(),
+        m, n, k,
+        sa[0], sb[0], sas[0], sas[1], sbs[0], sbs[1], sc[0], n_phase,
+        ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+        st.data_ptr(), stream,
+    )
+    if cplan is None:
+        rc = lib.b200_fp8_mm(*args)
+    else:
+        rc = lib.b200_fp8_mm_planned(*args, ctypes.byref(cplan))
     if rc != 0:
         raise Fp8MmError(rc, f"M={m} N={n} K={k}")
     if check:
