@@ -49,9 +49,6 @@ namespace {
 constexpr int kBlockM = 128;  // rows of C per CTA
 constexpr int kBlockK = 128;  // bytes of e4m3 per row of a stage = one scale block = one 128B swizzle row
 constexpr int kMmasPerBlock = 4;  // K = 32 per instruction
-constexpr int kNumEpiWarps = 8;
-constexpr int kNumEpiThreads = kNumEpiWarps * 32;
-constexpr int kNumThreads = 128 + kNumEpiThreads;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kCounterBytes = 4096;
 constexpr int kMaxCounters = kCounterBytes / 4;
@@ -61,10 +58,6 @@ constexpr int kStoreBufBytes = kBlockM * kStoreBoxCols * 2;      // one staging 
 constexpr int kScaleGroup = 4;                                   // K blocks per scale-ring slot
 constexpr int kScaleSlots = 4;                                   // ring depth (16 K blocks)
 constexpr int kScaleSlotFloats = kBlockM * kScaleGroup + 4 * kScaleGroup;  // a[128][4] + b[4][4]
-// Register split after setmaxnreg (light: producer / MMA / loader warps, heavy: promotion warps).
-// 128 * light + 256 * heavy = 384 * 168, the allocation the CTA is launched with.
-constexpr int kRegsLightWide = 72, kRegsHeavyWide = 216;  // block_n 256: 128 accumulators per thread
-constexpr int kRegsLight = 104, kRegsHeavy = 200;         // narrower tiles
 
 struct KernelParams {
   const float* a_scale;
@@ -340,8 +333,9 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&v)[64]) {
       : "memory");
 }
 
+template <int THREADS>
 __device__ __forceinline__ void epi_bar_sync() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiThreads) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
 }
 
 // Two fp32 accumulators live in one 64-bit register: acc.{lo,hi} += p.{0,1} * s.{lo,hi} with one
@@ -397,7 +391,20 @@ struct TileCfg {
   static constexpr int kTmemBufs = (BN <= 128) ? 4 : 2;
   static constexpr int kTmemColsUsed = kTmemBufs * BN;
   static constexpr int kTmemCols = kTmemColsUsed <= 256 ? 256 : 512;  // power of two >= 32
-  static constexpr int kColsPerThread = BN / 2;                        // two promotion warpgroups
+  // Promotion warps: groups of four (one per TMEM lane quarter), each group owning a share of the
+  // tile's columns. Two groups everywhere: a third group for the 192-wide tile (64 columns per
+  // thread instead of 96) was measured 6-15 % slower, more warps meaning more shared-memory
+  // barrier traffic on an already saturated shared-memory path.
+  static constexpr int kEpiWarps = 8;
+  static constexpr int kEpiGroups = kEpiWarps / 4;
+  static constexpr int kEpiThreads = kEpiWarps * 32;
+  static constexpr int kThreads = 128 + kEpiThreads;
+  static constexpr int kColsPerThread = BN / kEpiGroups;
+  // Register split after setmaxnreg (light: producer / MMA / loader warps, heavy: promotion warps):
+  // 128 * light + kEpiThreads * heavy is at most the allocation the CTA is launched with
+  // (384 x 168 or 512 x 128 registers).
+  static constexpr int kRegsLight = (kEpiWarps == 12) ? 56 : (BN == 256 ? 72 : 104);
+  static constexpr int kRegsHeavy = (kEpiWarps == 12) ? 152 : (BN == 256 ? 216 : 200);
   // Columns fetched from TMEM per tcgen05.ld: as wide as the registers allow without spilling
   // next to the accumulators (a spill in this loop costs hundreds of clocks: local memory shares
   // the saturated shared-memory path). tcgen05.wait::ld waits for every outstanding fetch, so
@@ -437,7 +444,7 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
 // ---------------------------------------------------------------------------------------------
 
 template <int BN, bool PAIR>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__((TileCfg<BN, PAIR>::kThreads), 1)
 fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const __grid_constant__ CUtensorMap tmap_c, const KernelParams p) {
   using Cfg = TileCfg<BN, PAIR>;
@@ -467,12 +474,12 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
       // one arrive.expect_tx per producing CTA + one release per promotion warp (of both CTAs)
-      mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1) * (1 + kNumEpiWarps));
+      mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1) * (1 + Cfg::kEpiWarps));
       mbar_init(smem_u32(&done_bar[s]), 1);  // the MMA thread's commit
     }
     for (int s = 0; s < kScaleSlots; ++s) {
       mbar_init(smem_u32(&scale_full_bar[s]), 32);
-      mbar_init(smem_u32(&scale_empty_bar[s]), kNumEpiWarps);
+      mbar_init(smem_u32(&scale_empty_bar[s]), Cfg::kEpiWarps);
     }
     *abort_flag = 0;
     *last_flag = 0;
@@ -507,7 +514,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   const int work_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(BN == 256 ? kRegsLightWide : kRegsLight));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::kRegsLight));
     if (warp == 0) {
       // ---------------- TMA producer ----------------
       if (lane == 0) {
@@ -621,10 +628,10 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     }
   } else {
     // ---------------- promotion + store ----------------
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(BN == 256 ? kRegsHeavyWide : kRegsHeavy));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::kRegsHeavy));
     const int ew = warp - 4;
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) belong to warps with this id mod 4
-    const int half = ew >> 2;      // which half of the tile's columns
+    const int half = ew >> 2;      // column group of this warp: which share of the tile's columns
     const int row_in_tile = quarter * 32 + lane;
     const int col_base = half * Cfg::kColsPerThread;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
@@ -807,16 +814,16 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               make_float4(acc[2 * j].x, acc[2 * j].y, acc[2 * j + 1].x, acc[2 * j + 1].y);
         }
         __threadfence();
-        epi_bar_sync();
+        epi_bar_sync<Cfg::kEpiThreads>();
         if (epi_tid == 0) {
           const int prev = atomicAdd(p.counters + unit, 1);
           const int last = (prev == p.split_k - 1) ? 1 : 0;
           if (last) p.counters[unit] = 0;  // leave the counters zero for the next launch
           *last_flag = last;
         }
-        epi_bar_sync();
+        epi_bar_sync<Cfg::kEpiThreads>();
         const int is_last = *last_flag;
-        epi_bar_sync();  // everyone has read the flag before thread 0 can overwrite it
+        epi_bar_sync<Cfg::kEpiThreads>();  // everyone has read the flag before thread 0 can overwrite it
         if (is_last) {
           __threadfence();
           const float4* base = reinterpret_cast<const float4*>(unit_base);
@@ -855,7 +862,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   if (warp >= 4) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");  // none in flight past here
     // the staging buffers must outlive the bulk stores that read them
-    if ((threadIdx.x & 127) == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if ((threadIdx.x & 127) == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // each group's issuer
   }
   // Teardown: every role has left its loop (normally or through an expired wait). In a pair no
   // CTA may exit while its peer can still signal its barriers or use its shared memory.
@@ -925,12 +932,18 @@ bool encode_output_map(CUtensorMap* map, void* base, int M, int N, long long ldc
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+int epi_warps_for(int block_n) {
+  (void)block_n;
+  return 8;  // keep in step with TileCfg::kEpiWarps
+}
+
 int smem_bytes_for(int block_n, int stages, int pair, int store_bufs) {
   const int stage = kBlockM * kBlockK + (pair ? block_n / 2 : block_n) * kBlockK;
   int bytes = stages * stage + kScaleSlots * kScaleSlotFloats * 4 + 512 /* barriers and flags */ +
               1024 /* alignment slack */;
-  // staging of c for the TMA store: two warpgroups x store_bufs buffers, 1024-byte aligned
-  if (store_bufs > 0) bytes += 1024 + 2 * store_bufs * kStoreBufBytes;
+  // staging of c for the TMA store: one area of store_bufs buffers per group of four promotion
+  // warps, 1024-byte aligned
+  if (store_bufs > 0) bytes += 1024 + (epi_warps_for(block_n) / 4) * store_bufs * kStoreBufBytes;
   return bytes;
 }
 
@@ -1190,7 +1203,7 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(static_cast<unsigned>(pl.grid), 1, 1);
-  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(128 + 32 * epi_warps_for(pl.block_n)), 1, 1);
   cfg.dynamicSmemBytes = static_cast<size_t>(pl.smem_bytes);
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[1];

@@ -104,8 +104,8 @@ class ClockSampler:
             for name, val in zip(names, r[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        # keep the samples taken under load: the upper half of the observed clocks
-        sm_load = sorted(sm)[len(sm) // 2:] if sm else []
+        # the first samples precede the warm-up: drop the leading quarter
+        sm_load = sm[len(sm) // 4:] if len(sm) >= 4 else sm
         return {"sm_mhz": statistics.median(sm_load) if sm_load else None,
                 "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
 
@@ -242,7 +242,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    m, n, k = HEADLINE
+    m, n, k = HEADLINE if not args.shape else tuple(int(x) for x in args.shape.split(","))
     spec = pkg.shard_spec(n, world, rank)
     n_loc = spec.n_local
     set_bytes = m * k + n_loc * k + 2 * m * n_loc
@@ -267,6 +267,7 @@ def run_ours(args):
         sampler.start()
     ms_local = time_launches(fns, args.steps, args.warmup)
     barrier()
+    clocks = sampler.stop() if sampler else None  # samples cover the timed GEMM loop only
     ms = max_over_ranks(ms_local)
     check_device_status(dev)
 
@@ -287,7 +288,6 @@ def run_ours(args):
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
     _ = time.perf_counter() - t0
     barrier()
-    clocks = sampler.stop() if sampler else None
     h2d = sum(t.numel() * t.element_size() for t in (ha, hb, has_, hbs))
     d2h = hc.numel() * hc.element_size()
 
@@ -300,7 +300,7 @@ def run_ours(args):
     per_shape = []
     cpu_baseline = None
     if rank == 0 and world == 1:
-        if not args.no_sweep:
+        if not args.no_sweep and not args.shape:
             shapes = list(NAMED_CONFIGS) + [(mm, nn, kk) for mm in SWEEP_M for (nn, kk) in SWEEP_NK]
             for (mm, nn, kk) in shapes:
                 # enough rotating input/output sets that consecutive launches do not find their
@@ -341,7 +341,7 @@ def run_ours(args):
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "e4m3fn x e4m3fn -> fp32 accumulate -> bf16", "data": "synthetic",
-            "config": {"workload": "fp8_block_scaled_gemm M=8192 N=4608 K=7168",
+            "config": {"workload": f"fp8_block_scaled_gemm M={m} N={n} K={k}",
                        "sharding": f"b/b_scale over N, {n_loc} columns per GPU, c left sharded",
                        "plan": f"{'2x' if plan.cta_pair else ''}128x{plan.block_n} split{plan.split_k} "
                                f"stages{plan.stages} grid{plan.grid}",
@@ -374,6 +374,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-shape sweep (N=1 only)")
+    ap.add_argument("--shape", default="", help="M,N,K of another workload (for small profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
