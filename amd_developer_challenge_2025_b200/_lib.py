@@ -16,6 +16,8 @@ ABI_VERSION = 2
 EXPORTS = (
     "b200_fp8_mm",
     "b200_fp8_mm_planned",
+    "b200_fp8_mm_static_scratch",
+    "b200_fp8_mm_static_scratch_limit",
     "b200_fp8_mm_workspace_bytes",
     "b200_fp8_mm_plan_workspace_bytes",
     "b200_fp8_mm_describe",
@@ -65,6 +67,11 @@ def load() -> ctypes.CDLL:
     lib.b200_fp8_mm.restype = ctypes.c_int
     lib.b200_fp8_mm_planned.argtypes = _GEMM_ARGS + [ctypes.POINTER(CPlan)]
     lib.b200_fp8_mm_planned.restype = ctypes.c_int
+    # the same argument list without the (workspace, workspace_bytes) pair
+    lib.b200_fp8_mm_static_scratch.argtypes = _GEMM_ARGS[:16] + _GEMM_ARGS[18:]
+    lib.b200_fp8_mm_static_scratch.restype = ctypes.c_int
+    lib.b200_fp8_mm_static_scratch_limit.argtypes = []
+    lib.b200_fp8_mm_static_scratch_limit.restype = ctypes.c_size_t
     lib.b200_fp8_mm_workspace_bytes.argtypes = [ctypes.c_int] * 3
     lib.b200_fp8_mm_workspace_bytes.restype = ctypes.c_size_t
     lib.b200_fp8_mm_plan_workspace_bytes.argtypes = [ctypes.c_int] * 3 + [ctypes.POINTER(CPlan)]

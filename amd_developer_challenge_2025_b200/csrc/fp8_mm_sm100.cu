@@ -1223,6 +1223,39 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   return B200_FP8_MM_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Scratch that lives in the library image, for callers that may not allocate
+// ---------------------------------------------------------------------------------------------
+
+// Split-K plans need scratch memory (tile counters + fp32 partial planes). Some callers have no
+// way to provide it: code that runs where cudaMalloc is off limits (a plug-in whose enqueue hook
+// is handed only input and output pointers, a serving loop that must not take the allocator's
+// implicit device synchronisation, anything that runs while the process's memory pools are
+// frozen). For them the scratch is this fixed array in the library's device image. Every GPU
+// that loads the library carries these 8 MiB until the process exits.
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device. In host code the array's name is only
+// a handle for the runtime, not an address a kernel could use, so the address is asked for once
+// per device (with that device current) and remembered.
+int static_scratch_address(void** out) {
+  static void* cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_FP8_MM_ERR_DRIVER;
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      return B200_FP8_MM_ERR_DRIVER;
+    }
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return B200_FP8_MM_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -1242,6 +1275,34 @@ int b200_fp8_mm_planned(const void* a, const void* b, const float* a_scale, cons
   return run(a, b, a_scale, b_scale, c, M, N, K, lda, ldb, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, workspace,
              workspace_bytes, device_status, stream, forced);
 }
+
+int b200_fp8_mm_static_scratch(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c,
+                               int M, int N, int K, long long lda, long long ldb, long long sa_m, long long sa_k,
+                               long long sb_n, long long sb_k, long long ldc, int n_phase, int* device_status,
+                               void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return B200_FP8_MM_ERR_SHAPE;
+  const int sm_count = device_sm_count();
+  if (sm_count <= 0) return B200_FP8_MM_ERR_DRIVER;
+  b200_fp8_mm_plan pl;
+  choose_plan(M, N, K, sm_count, nullptr, &pl);
+  const size_t need = plan_workspace_bytes(pl);
+  if (need > kStaticScratchBytes) return B200_FP8_MM_ERR_SCRATCH_LIMIT;
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);  // first call on a device looks the address up
+  if (rc != B200_FP8_MM_OK) return rc;
+  if (need > 0) {
+    // The array still holds whatever the previous call left; the tile counters have to start at
+    // zero (a launch that was cut short would leave them mid-count).
+    if (cudaMemsetAsync(scratch, 0, kCounterBytes, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return B200_FP8_MM_ERR_LAUNCH;
+    }
+  }
+  return run(a, b, a_scale, b_scale, c, M, N, K, lda, ldb, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, scratch,
+             kStaticScratchBytes, device_status, stream, nullptr);
+}
+
+size_t b200_fp8_mm_static_scratch_limit(void) { return kStaticScratchBytes; }
 
 size_t b200_fp8_mm_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return 0;
@@ -1279,6 +1340,9 @@ const char* b200_fp8_mm_strerror(int code) {
     case B200_FP8_MM_ERR_PLAN: return "forced plan not supported";
     case B200_FP8_MM_ERR_DRIVER: return "no sm_100 device or tensor-map encode failed";
     case B200_FP8_MM_ERR_LAUNCH: return "kernel launch failed";
+    case B200_FP8_MM_ERR_SCRATCH_LIMIT:
+      return "this problem needs more scratch than the 8 MiB built into the library; use b200_fp8_mm with a "
+             "caller-provided workspace";
     default: return "unknown error";
   }
 }

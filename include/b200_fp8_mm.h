@@ -36,7 +36,9 @@ enum {
   B200_FP8_MM_ERR_WORKSPACE = 6,   /* workspace missing or too small for the plan  */
   B200_FP8_MM_ERR_PLAN = 7,        /* a forced plan is not one the kernels support */
   B200_FP8_MM_ERR_DRIVER = 8,      /* tensor-map encode failed / no sm_100 device  */
-  B200_FP8_MM_ERR_LAUNCH = 9       /* cudaLaunchKernelEx returned an error         */
+  B200_FP8_MM_ERR_LAUNCH = 9,      /* cudaLaunchKernelEx returned an error         */
+  B200_FP8_MM_ERR_SCRATCH_LIMIT = 10 /* b200_fp8_mm_static_scratch: the plan needs more
+                                        than the scratch built into the library     */
 };
 
 /* Device-side status word values (written to device_status[0]; [1] holds the
@@ -111,6 +113,41 @@ int b200_fp8_mm_planned(const void* a, const void* b, const float* a_scale, cons
                         void* workspace, size_t workspace_bytes,
                         int* device_status, void* stream,
                         const b200_fp8_mm_plan* forced);
+
+/*
+ * The same GEMM for callers that cannot allocate device memory. (No counterpart in the
+ * reference: its launcher gets its split-K scratch from torch.empty on every call.)
+ *
+ * Who needs it: code that is given input and output pointers and nothing else, and for which
+ * cudaMalloc is not an option - an engine plug-in's enqueue hook, a latency-critical serving
+ * loop that must not take the implicit device synchronisation of the allocator, a process
+ * whose memory pools are frozen after start-up. b200_fp8_mm makes such a caller bring a
+ * workspace for split-K plans; this entry point brings its own instead: a fixed 8 MiB array
+ * inside the library's device image (b200_fp8_mm_static_scratch_limit() returns the size).
+ * Every GPU that loads the library holds those 8 MiB until the process exits.
+ *
+ * Arguments as for b200_fp8_mm, without the workspace pair. It never calls cudaMalloc,
+ * cudaFree or any allocating library routine. Problems whose plan needs more scratch than the
+ * array holds are refused with B200_FP8_MM_ERR_SCRATCH_LIMIT (nothing is launched); plans that
+ * do not split K need no scratch and always fit.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ * with that device current) and keeps it; make that first call outside any stream capture.
+ * All calls share the one array, which keeps what the previous call left in it: the entry
+ * point zeroes the tile counters on `stream` before each launch that uses them, and two calls
+ * that can overlap on the GPU (different streams, no dependency) would race on it - serialise
+ * them, or use b200_fp8_mm with separate workspaces.
+ */
+int b200_fp8_mm_static_scratch(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c,
+                               int M, int N, int K,
+                               long long lda, long long ldb,
+                               long long sa_m, long long sa_k,
+                               long long sb_n, long long sb_k,
+                               long long ldc, int n_phase,
+                               int* device_status, void* stream);
+
+/* Size in bytes of the scratch array b200_fp8_mm_static_scratch uses. */
+size_t b200_fp8_mm_static_scratch_limit(void);
 
 /* Workspace the plan chosen by b200_fp8_mm for (M,N,K) needs, in bytes (0 when it does
  * not split K). Replaces
