@@ -1,0 +1,136 @@
+"""Harness-style runner for the FP8 block-scaled GEMM operator.
+
+The reference is exercised by an external harness that reads a spec file of lines such as
+
+    m: 1024; n: 1536; k: 7168; seed: 8135
+
+(reference README.md:62-82) and calls `custom_kernel` in `test` or `benchmark` mode
+(README.md:85-100). That harness, its input generator and its checker are not part of the
+reference project; this runner offers the same workflow on top of this package's own pieces:
+
+    python -m amd_developer_challenge_2025_b200.runner benchmark spec.txt
+    python -m amd_developer_challenge_2025_b200.runner test spec.txt
+    python -m amd_developer_challenge_2025_b200.runner benchmark --competition-shapes
+
+`test` compares the operator with an fp32 dequantise-then-matmul written in torch on the GPU
+(what the reference's own first script computes, 1-amd-fp8-mm/0-amd-fp8-mm-new-begins.py:17-49,
+85-89) with rtol=2e-2, atol=1e-3 on the bf16 output. `benchmark` times the call with CUDA events
+and prints one JSON line per spec line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import re
+import statistics
+import sys
+
+import torch
+
+from .fp8_mm import check_device_status, describe
+from .inputs import make_inputs
+from .submission import custom_kernel
+
+# The competition's benchmark grid as the reference describes it (README.md:62-82): two values of m
+# times nine (n, k) pairs. The harness's own seeds belong to its task files and are not reproduced;
+# seeds here are derived from the shape.
+COMPETITION_M = (1024, 6144)
+COMPETITION_NK = ((1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
+                  (512, 7168), (4096, 512))
+
+
+def competition_cases():
+    return [(m, n, k, (m * 31 + n * 17 + k) % 100003) for m in COMPETITION_M for (n, k) in COMPETITION_NK]
+
+
+RTOL, ATOL = 2e-2, 1e-3
+
+
+def parse_spec(text: str):
+    """[(m, n, k, seed)] from `m: ..; n: ..; k: ..; seed: ..` lines; blank lines and # comments skipped."""
+    cases = []
+    for raw in text.splitlines():
+        line = raw.split("#", 1)[0].strip()
+        if not line:
+            continue
+        fields = dict((k.strip(), v.strip()) for k, v in (part.split(":", 1) for part in line.split(";") if part.strip()))
+        try:
+            cases.append((int(fields["m"]), int(fields["n"]), int(fields["k"]), int(fields.get("seed", 0))))
+        except (KeyError, ValueError) as e:
+            raise ValueError(f"bad spec line: {raw!r}") from e
+    return cases
+
+
+def dequant_reference(a, b, a_scale, b_scale):
+    """fp32 dequantise-then-matmul on the tensors' own device, rounded to bf16."""
+    n = b.shape[0]
+    rows = torch.arange(n, device=b.device) // 128
+    a32 = a.float() * a_scale.repeat_interleave(128, dim=1)
+    b32 = b.float() * b_scale[rows].repeat_interleave(128, dim=1)
+    return (a32 @ b32.T).to(torch.bfloat16)
+
+
+def run_test(cases, device="cuda"):
+    results = []
+    for (m, n, k, seed) in cases:
+        data = make_inputs(m, n, k, seed, device=device)
+        out = custom_kernel(data)
+        check_device_status(device)
+        ref = dequant_reference(*data[:4]).float()
+        err = (out.float() - ref).abs()
+        ok = bool((err <= ATOL + RTOL * ref.abs()).all().item())
+        results.append({"m": m, "n": n, "k": k, "seed": seed, "pass": ok, "max_abs_err": float(err.max().item())})
+        print(json.dumps(results[-1]), flush=True)
+    return results
+
+
+def run_benchmark(cases, device="cuda", reps=50, warmup=5):
+    results = []
+    for (m, n, k, seed) in cases:
+        data = make_inputs(m, n, k, seed, device=device)
+        for _ in range(warmup):
+            custom_kernel(data)
+        check_device_status(device)
+        times = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            custom_kernel(data)
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3)
+        us = statistics.median(times)
+        plan = describe(m, n, k)
+        results.append({"m": m, "n": n, "k": k, "seed": seed, "us_median": round(us, 2),
+                        "us_best": round(min(times), 2), "tflops": round(2.0 * m * n * k / us / 1e6, 1),
+                        "plan": f"{'2x' if plan.cta_pair else ''}128x{plan.block_n} split{plan.split_k}"})
+        print(json.dumps(results[-1]), flush=True)
+    geo = statistics.geometric_mean(r["us_median"] for r in results) if results else 0.0
+    print(json.dumps({"geomean_us": round(geo, 2), "cases": len(results)}), flush=True)
+    return results
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("mode", choices=("test", "benchmark"))
+    ap.add_argument("spec", nargs="?", help="spec file; omit with --competition-shapes")
+    ap.add_argument("--competition-shapes", action="store_true", help="the 2 x 9 shape grid the reference describes")
+    ap.add_argument("--device", default="cuda")
+    args = ap.parse_args(argv)
+    if args.competition_shapes:
+        cases = competition_cases()
+    elif args.spec:
+        with open(args.spec) as f:
+            cases = parse_spec(f.read())
+    else:
+        ap.error("give a spec file or --competition-shapes")
+    if not torch.cuda.is_available():
+        sys.exit("the operator needs a CUDA device: there is no CPU path")
+    if args.mode == "test":
+        results = run_test(cases, args.device)
+        sys.exit(0 if all(r["pass"] for r in results) else 1)
+    run_benchmark(cases, args.device)
+
+
+if __name__ == "__main__":
+    main()

@@ -98,3 +98,14 @@ def test_product_never_imports_oracle():
             if f.endswith((".py", ".cu", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("oracle and", "").replace("CPU oracle", ""), f
+
+
+def test_runner_spec_parser_and_grid():
+    from amd_developer_challenge_2025_b200 import runner
+
+    cases = runner.parse_spec("m: 1024; n: 576 ; k: 7168; seed: 7\n\n# comment\nm: 8; n: 16; k: 128\n")
+    assert cases == [(1024, 576, 7168, 7), (8, 16, 128, 0)]
+    with pytest.raises(ValueError):
+        runner.parse_spec("m: 8; n: 16")
+    grid = runner.competition_cases()
+    assert len(grid) == 18 and all(k % 128 == 0 for (_, _, k, _) in grid)
