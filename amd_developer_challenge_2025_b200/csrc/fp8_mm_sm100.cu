@@ -18,7 +18,8 @@
 //               collects the promotion warps' release of the TMEM buffer that K block will
 //               overwrite (stage s always pairs with buffer s mod buffers: the ring depth is a
 //               multiple of the buffer count)
-//   warp 2      allocates / frees TMEM
+//   warp 2      allocates / frees TMEM; its first lane is a second MMA issuer (the two issuers take
+//               alternate K blocks)
 //   warp 3      scale loader: cp.async of the a_scale / b_scale values of FOUR K blocks at a time
 //               into a small shared-memory ring, up to 16 K blocks ahead
 //   warps 4-11  promotion + store: tcgen05.ld the partial, fma into register accumulators with
@@ -75,6 +76,7 @@ struct KernelParams {
   int vec_store;  // 1 when c, ldc and N allow 16-byte stores
   int stages;
   int tmem_bufs;  // TMEM partial buffers in use: divides stages, at most TileCfg::kTmemBufs
+  int issuers;     // MMA-issuing threads in use: 1 or 2
   int store_bufs;  // staging buffers per promotion warpgroup for the TMA store of c: 0 (plain stores), 1 or 2
 };
 
@@ -544,22 +546,40 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         }
       }
       __syncwarp();
-    } else if (warp == 1) {
-      // ---------------- MMA issuer (the leader CTA of a pair issues for both) ----------------
-      if (lane == 0 && cta_rank == 0) {
+    } else if (warp == 1 || warp == 2) {
+      // ---------------- MMA issuers (the leader CTA of a pair issues for both) ----------------
+      // Two threads, one in each warp, take alternate K blocks. A K block's MMAs go to a TMEM buffer of
+      // their own, so the two streams need no ordering between them; one thread alone spends about
+      // 700 clocks per K block on its barrier wait and on issuing (an MMA costs the issuing thread
+      // roughly 100 clocks), more than the tensor pipe needs to execute the block.
+      if (lane == 0 && cta_rank == 0 && warp - 1 < p.issuers) {
         constexpr uint32_t idesc = make_idesc(Cfg::kTileM, BN);
-        int stage = 0, buf = 0;
+        const int me = warp - 1;
+        // Both issuers walk every K block and keep the ring position with increments only (no
+        // division on this thread: its scalar work is on the critical path); each issues for the
+        // K blocks whose turn it is.
+        int stage = 0, buf = 0, turn = 0;
         uint32_t phase = 0;
         bool ok = true;
         for (int w = work_first; w < total_work && ok; w += work_step) {
           const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
           for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
-            const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+            const bool mine = (turn == me);
+            if (++turn == p.issuers) turn = 0;
+            const int my_stage = stage, my_buf = buf;
+            const uint32_t my_phase = phase;
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            if (++buf == nbufs) buf = 0;
+            if (!mine) continue;
+            const uint32_t sa = smem_u32(smem + my_stage * Cfg::kStageBytes);
             const uint32_t a_lo = smem_desc_lo(sa);
             const uint32_t b_lo = smem_desc_lo(sa + Cfg::kStageBytesA);
-            const uint32_t d_addr = tmem_base + static_cast<uint32_t>(buf * BN);
+            const uint32_t d_addr = tmem_base + static_cast<uint32_t>(my_buf * BN);
             // operands landed AND the TMEM buffer of this K block drained (see the promotion warps)
-            if (!mbar_wait(smem_u32(&full_bar[stage]), phase, ctx, 0x300 | stage)) {
+            if (!mbar_wait(smem_u32(&full_bar[my_stage]), my_phase, ctx, 0x300 | my_stage)) {
               ok = false;
               break;
             }
@@ -569,12 +589,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               // 32 bytes further along K inside the 128-byte swizzle row = +2 in 16-byte units
               umma_f8<PAIR>(d_addr, a_lo + 2u * k, b_lo + 2u * k, kSmemDescHi, idesc, k > 0 ? 1u : 0u);
             }
-            umma_commit<PAIR>(smem_u32(&done_bar[stage]));
-            if (++stage == stages) {
-              stage = 0;
-              phase ^= 1u;
-            }
-            if (++buf == nbufs) buf = 0;
+            umma_commit<PAIR>(smem_u32(&done_bar[my_stage]));
           }
         }
       }
@@ -1171,6 +1186,10 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   kp.stages = pl.stages;
   kp.tmem_bufs = tmem_bufs_in_use(pl.block_n, pl.stages);
   kp.store_bufs = store_bufs;
+  {
+    const char* e = getenv("B200_FP8_MM_ISSUERS");  // tuning knob
+    kp.issuers = (e && atoi(e) == 1) ? 1 : 2;
+  }
   {
     // Tile rows per raster group: the tiles running at one time form a block as square as possible.
     const int units = pl.cta_pair ? sm_count / 2 : sm_count;
