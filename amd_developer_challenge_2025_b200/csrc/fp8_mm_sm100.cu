@@ -548,10 +548,10 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       __syncwarp();
     } else if (warp == 1 || warp == 2) {
       // ---------------- MMA issuers (the leader CTA of a pair issues for both) ----------------
-      // Two threads, one in each warp, take alternate K blocks. A K block's MMAs go to a TMEM buffer of
-      // their own, so the two streams need no ordering between them; one thread alone spends about
-      // 700 clocks per K block on its barrier wait and on issuing (an MMA costs the issuing thread
-      // roughly 100 clocks), more than the tensor pipe needs to execute the block.
+      // Up to two threads, one in each warp, take alternate K blocks. A K block's MMAs go to a TMEM
+      // buffer of their own, so the two streams need no ordering between them; one thread alone spends
+      // about 700 clocks per K block on its barrier wait and on issuing (an MMA costs the issuing
+      // thread roughly 100 clocks), more than the tensor pipe needs for a narrow tile's block.
       if (lane == 0 && cta_rank == 0 && warp - 1 < p.issuers) {
         constexpr uint32_t idesc = make_idesc(Cfg::kTileM, BN);
         const int me = warp - 1;
@@ -1000,21 +1000,21 @@ size_t plan_workspace_bytes(const b200_fp8_mm_plan& pl) {
 
 // Tile/launch selection: a pure function of the problem and the SM count.
 //
-// Cost model, in SM clocks, fitted by least squares (median error 3 %) to CUDA-event timings of every
-// plan over the 36 benchmark shapes on B200. Per tile width 64/128/192/256: clocks per K block (the
-// hand-shake between the MMA warp and the promotion warps bounds it from below at about 600, not the
-// tensor pipe), clocks per tile for the bf16 output, and for split-K a constant plus a per-range
-// cost of the fp32 round trip and the last-arriver reduction.
+// Cost model, in SM clocks, fitted by least squares (median error 2-3 %) to CUDA-event timings of every
+// plan over the 36 benchmark shapes on B200. Per tile width 64/128/192/256: clocks per K block (bounded
+// by the promotion warps' chain of barrier probe, TMEM fetch and fmas, not by the tensor pipe), clocks
+// per tile for the bf16 output, and for split-K a constant plus a per-range cost of the fp32 round
+// trip and the last-arriver reduction.
 struct WidthCost {
   double per_kblock, per_tile, split_const, per_split;
 };
 
 WidthCost width_cost(int bn) {
   switch (bn) {
-    case 64: return {640.0, 1300.0, 11000.0, 650.0};
-    case 128: return {680.0, 2200.0, 21000.0, 750.0};
-    case 192: return {840.0, 3250.0, 30000.0, 1700.0};
-    default: return {1300.0, 4300.0, 42500.0, 2900.0};
+    case 64: return {400.0, 1850.0, 11700.0, 400.0};
+    case 128: return {585.0, 2500.0, 19500.0, 900.0};
+    case 192: return {815.0, 3300.0, 30000.0, 1300.0};
+    default: return {1330.0, 4400.0, 41500.0, 2650.0};
   }
 }
 
@@ -1186,10 +1186,9 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   kp.stages = pl.stages;
   kp.tmem_bufs = tmem_bufs_in_use(pl.block_n, pl.stages);
   kp.store_bufs = store_bufs;
-  {
-    const char* e = getenv("B200_FP8_MM_ISSUERS");  // tuning knob
-    kp.issuers = (e && atoi(e) == 1) ? 1 : 2;
-  }
+  // Two issuing threads pay off where the MMAs are short (narrow tiles: 25 % faster at block_n 64,
+  // 10 % at 128); the wide tiles are bound by the promotion warps and run 1 % better with one.
+  kp.issuers = pl.block_n <= 128 ? 2 : 1;
   {
     // Tile rows per raster group: the tiles running at one time form a block as square as possible.
     const int units = pl.cta_pair ? sm_count / 2 : sm_count;
