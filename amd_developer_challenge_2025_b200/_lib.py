@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # B200_FP8_MM_LIB selects another build of the same library (e.g. one made with extra nvcc flags).
 LIB_PATH = os.environ.get("B200_FP8_MM_LIB") or os.path.join(HERE, "lib", "libb200fp8mm.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 # Every symbol include/b200_fp8_mm.h declares.
 EXPORTS = (
@@ -37,6 +37,7 @@ class CPlan(ctypes.Structure):
         ("tiles", ctypes.c_int),
         ("smem_bytes", ctypes.c_int),
         ("store_bufs", ctypes.c_int),
+        ("full_tiles", ctypes.c_int),
     ]
 
 

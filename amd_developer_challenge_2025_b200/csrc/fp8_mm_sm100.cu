@@ -71,6 +71,7 @@ struct KernelParams {
   int M, N, K;
   int n_phase;
   int tiles_m, tiles_n, split_k, kblocks;
+  int full_tiles;  // tiles [0, full_tiles) run unsplit; the rest are split split_k ways along K
   int raster_group;
   int b_scale_rows;
   int vec_store;  // 1 when c, ldc and N allow 16-byte stores
@@ -417,15 +418,26 @@ struct TileCfg {
 };
 
 struct WorkItem {
-  int m0, n0, tile, split, kb_begin, kb_end;
+  int m0, n0, tile, split, nsplit, kb_begin, kb_end;
 };
 
 // Work item w -> tile and K range. Tiles are walked in groups of raster_group tile rows, column
 // by column inside a group, so that the CTAs running at one time share A and B tiles in L2.
 __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, int tile_m, int block_n) {
   WorkItem it;
-  it.split = w % p.split_k;
-  const int t = w / p.split_k;
+  int t;
+  if (w < p.full_tiles) {
+    t = w;
+    it.split = 0;
+    it.nsplit = 1;
+  } else {
+    // The tail: tiles that would fill only part of a last wave are cut along K so that every CTA
+    // gets a share of them.
+    const int r = w - p.full_tiles;
+    t = p.full_tiles + r / p.split_k;
+    it.split = r % p.split_k;
+    it.nsplit = p.split_k;
+  }
   it.tile = t;
   const int per_group = p.raster_group * p.tiles_n;
   const int group = t / per_group;
@@ -436,8 +448,8 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
   const int tn = within / gsize;
   it.m0 = tm * tile_m;
   it.n0 = tn * block_n;
-  it.kb_begin = static_cast<int>((static_cast<long long>(it.split) * p.kblocks) / p.split_k);
-  it.kb_end = static_cast<int>((static_cast<long long>(it.split + 1) * p.kblocks) / p.split_k);
+  it.kb_begin = static_cast<int>((static_cast<long long>(it.split) * p.kblocks) / it.nsplit);
+  it.kb_end = static_cast<int>((static_cast<long long>(it.split + 1) * p.kblocks) / it.nsplit);
   return it;
 }
 
@@ -511,7 +523,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  const int total_work = p.tiles_m * p.tiles_n * p.split_k;
+  const int total_work = p.full_tiles + (p.tiles_m * p.tiles_n - p.full_tiles) * p.split_k;
   const int work_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int work_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
@@ -755,7 +767,53 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
       for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) acc[j] = unpack2(acc2[j]);
       const int col0 = it.n0 + col_base;  // first column of this thread inside (the shard of) c
-      if (p.split_k == 1 && p.store_bufs > 0) {
+      bool do_store = true;
+      if (it.nsplit > 1) {
+        // Split-K: publish this K range's fp32 tile; the last CTA to arrive for the tile then sums the
+        // ranges in order 0..nsplit-1 (so the result does not depend on arrival order) and stores the
+        // tile like an unsplit one. Plane layout per (split tile, CTA of the pair, range): float4 index
+        // (col/4)*128 + row, so that a warp's accesses cover 512 contiguous bytes.
+        const size_t plane_floats = static_cast<size_t>(kBlockM) * BN;
+        const size_t unit = static_cast<size_t>(it.tile - p.full_tiles) * (PAIR ? 2 : 1) + cta_rank;
+        float* unit_base = p.partials + unit * p.split_k * plane_floats;
+        float4* mine = reinterpret_cast<float4*>(unit_base + static_cast<size_t>(it.split) * plane_floats);
+#pragma unroll
+        for (int j = 0; j < Cfg::kColsPerThread / 4; ++j) {
+          const int c4 = (col_base >> 2) + j;
+          mine[c4 * kBlockM + row_in_tile] =
+              make_float4(acc[2 * j].x, acc[2 * j].y, acc[2 * j + 1].x, acc[2 * j + 1].y);
+        }
+        __threadfence();
+        epi_bar_sync<Cfg::kEpiThreads>();
+        if (epi_tid == 0) {
+          const int prev = atomicAdd(p.counters + unit, 1);
+          const int last = (prev == it.nsplit - 1) ? 1 : 0;
+          if (last) p.counters[unit] = 0;  // leave the counters zero for the next launch
+          *last_flag = last;
+        }
+        epi_bar_sync<Cfg::kEpiThreads>();
+        do_store = (*last_flag != 0);
+        epi_bar_sync<Cfg::kEpiThreads>();  // everyone has read the flag before thread 0 can overwrite it
+        if (do_store) {
+          __threadfence();
+          const float4* base = reinterpret_cast<const float4*>(unit_base);
+#pragma unroll
+          for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+          for (int sp = 0; sp < it.nsplit; ++sp) {
+            // all of one range's loads are independent: they are in flight together
+            const float4* plane = base + static_cast<size_t>(sp) * (plane_floats / 4);
+#pragma unroll
+            for (int j = 0; j < Cfg::kColsPerThread / 4; ++j) {
+              const float4 t = __ldcg(plane + ((col_base >> 2) + j) * kBlockM + row_in_tile);
+              acc[2 * j].x += t.x;
+              acc[2 * j].y += t.y;
+              acc[2 * j + 1].x += t.z;
+              acc[2 * j + 1].y += t.w;
+            }
+          }
+        }
+      }
+      if (do_store && p.store_bufs > 0) {
         // bf16 tile -> swizzled staging -> TMA store, 32 columns at a time per warpgroup. The
         // 16-byte piece q of row r sits at r*64 + ((q ^ ((r >> 1) & 3)) * 16) (SWIZZLE_64B), which
         // spreads a warp's stores over all banks.
@@ -791,7 +849,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             tma_store_2d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
                          it.m0 + static_cast<int>(cta_rank) * kBlockM);
         }
-      } else if (p.split_k == 1) {
+      } else if (do_store) {
         if (row < p.M) {
           __nv_bfloat16* crow = p.c + static_cast<long long>(row) * p.ldc;
 #pragma unroll
@@ -809,63 +867,6 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               for (int e = 0; e < 4; ++e) {
                 if (col + 2 * e < p.N) crow[col + 2 * e] = __float2bfloat16_rn(acc[j * 4 + e].x);
                 if (col + 2 * e + 1 < p.N) crow[col + 2 * e + 1] = __float2bfloat16_rn(acc[j * 4 + e].y);
-              }
-            }
-          }
-        }
-      } else {
-        // Split-K: publish this K range's fp32 tile, then the last CTA to arrive for the tile
-        // sums the ranges in order 0..split_k-1 (so the result does not depend on arrival order).
-        // Plane layout per (tile, CTA of the pair, split): float4 index (col/4)*128 + row, so that
-        // a warp's store covers 512 contiguous bytes.
-        const size_t plane_floats = static_cast<size_t>(kBlockM) * BN;
-        const size_t unit = static_cast<size_t>(it.tile) * (PAIR ? 2 : 1) + cta_rank;
-        float* unit_base = p.partials + unit * p.split_k * plane_floats;
-        float4* mine = reinterpret_cast<float4*>(unit_base + static_cast<size_t>(it.split) * plane_floats);
-#pragma unroll
-        for (int j = 0; j < Cfg::kColsPerThread / 4; ++j) {
-          const int c4 = (col_base >> 2) + j;
-          mine[c4 * kBlockM + row_in_tile] =
-              make_float4(acc[2 * j].x, acc[2 * j].y, acc[2 * j + 1].x, acc[2 * j + 1].y);
-        }
-        __threadfence();
-        epi_bar_sync<Cfg::kEpiThreads>();
-        if (epi_tid == 0) {
-          const int prev = atomicAdd(p.counters + unit, 1);
-          const int last = (prev == p.split_k - 1) ? 1 : 0;
-          if (last) p.counters[unit] = 0;  // leave the counters zero for the next launch
-          *last_flag = last;
-        }
-        epi_bar_sync<Cfg::kEpiThreads>();
-        const int is_last = *last_flag;
-        epi_bar_sync<Cfg::kEpiThreads>();  // everyone has read the flag before thread 0 can overwrite it
-        if (is_last) {
-          __threadfence();
-          const float4* base = reinterpret_cast<const float4*>(unit_base);
-          if (row < p.M) {
-            __nv_bfloat16* crow = p.c + static_cast<long long>(row) * p.ldc;
-#pragma unroll 2
-            for (int j = 0; j < Cfg::kColsPerThread / 4; ++j) {
-              const int c4 = (col_base >> 2) + j;
-              float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int s = 0; s < p.split_k; ++s) {
-                const float4 t = __ldcg(base + static_cast<size_t>(s) * (plane_floats / 4) + c4 * kBlockM + row_in_tile);
-                sum.x += t.x;
-                sum.y += t.y;
-                sum.z += t.z;
-                sum.w += t.w;
-              }
-              const int col = col0 + j * 4;
-              if (p.vec_store && col + 4 <= p.N) {
-                uint2 o;
-                o.x = pack_bf16x2(sum.x, sum.y);
-                o.y = pack_bf16x2(sum.z, sum.w);
-                *reinterpret_cast<uint2*>(crow + col) = o;
-              } else {
-                if (col + 0 < p.N) crow[col + 0] = __float2bfloat16_rn(sum.x);
-                if (col + 1 < p.N) crow[col + 1] = __float2bfloat16_rn(sum.y);
-                if (col + 2 < p.N) crow[col + 2] = __float2bfloat16_rn(sum.z);
-                if (col + 3 < p.N) crow[col + 3] = __float2bfloat16_rn(sum.w);
               }
             }
           }
@@ -994,8 +995,9 @@ bool valid_block_n(int bn) { return bn == 64 || bn == 128 || bn == 192 || bn == 
 
 size_t plan_workspace_bytes(const b200_fp8_mm_plan& pl) {
   if (pl.split_k <= 1) return 0;
-  return static_cast<size_t>(kCounterBytes) + static_cast<size_t>(pl.tiles) * (pl.cta_pair ? 2 : 1) *
-                                                  pl.split_k * kBlockM * pl.block_n * sizeof(float);
+  return static_cast<size_t>(kCounterBytes) + static_cast<size_t>(pl.tiles - pl.full_tiles) *
+                                                  (pl.cta_pair ? 2 : 1) * pl.split_k * kBlockM * pl.block_n *
+                                                  sizeof(float);
 }
 
 // Tile/launch selection: a pure function of the problem and the SM count.
@@ -1011,37 +1013,57 @@ struct WidthCost {
 
 WidthCost width_cost(int bn) {
   switch (bn) {
-    case 64: return {400.0, 1850.0, 11700.0, 400.0};
-    case 128: return {585.0, 2500.0, 19500.0, 900.0};
-    case 192: return {815.0, 3300.0, 30000.0, 1300.0};
-    default: return {1330.0, 4400.0, 41500.0, 2650.0};
+    case 64: return {400.0, 1850.0, 6500.0, 750.0};
+    case 128: return {585.0, 2500.0, 9000.0, 1100.0};
+    case 192: return {815.0, 3300.0, 8500.0, 1000.0};
+    default: return {1330.0, 4400.0, 11000.0, 1500.0};
   }
 }
 
 struct Candidate {
-  int bn, pair, split;
+  int bn, pair, split, full_tiles;
   double cost;
 };
 
+// Three ways to lay a problem out, for one tile shape: every tile whole; every tile split along K
+// (few tiles, long K: the tiles alone would leave SMs idle); or whole tiles for the full waves and a
+// split-K tail for the tiles that would fill only part of a last wave.
 Candidate evaluate(int M, int N, int kblocks, int sm_count, int bn, int pair, int forced_split) {
   const int tiles = ceil_div(M, pair ? 2 * kBlockM : kBlockM) * ceil_div(N, bn);
   const int units = pair ? sm_count / 2 : sm_count;
-  int split = forced_split;
-  if (split == 0) {
-    split = 1;
-    if (tiles * 2 <= units && kblocks >= 8 && tiles * (pair ? 2 : 1) <= kMaxCounters) {
-      split = units / tiles;
-      if (split > kblocks / 4) split = kblocks / 4;
-      if (split > 16) split = 16;
-      if (split < 1) split = 1;
+  const WidthCost wc = width_cost(bn);
+  const int per_unit = pair ? 2 : 1;
+  auto cap_split = [&](int s) {
+    if (s > kblocks / 4) s = kblocks / 4;
+    if (s > 16) s = 16;
+    return s < 1 ? 1 : s;
+  };
+  Candidate best{bn, pair, 1, tiles, ceil_div(tiles, units) * (kblocks * wc.per_kblock + wc.per_tile)};
+  if (forced_split == 1 || kblocks < 8) {
+    if (pair) best.cost *= 1.04;
+    return best;
+  }
+  if (tiles * 2 <= units || (forced_split > 1 && tiles <= units)) {
+    // all tiles split
+    const int split = forced_split > 1 ? forced_split : cap_split(units / tiles);
+    if (split > 1 && tiles * per_unit <= kMaxCounters) {
+      const double cost = ceil_div(tiles * split, units) * (ceil_div(kblocks, split) * wc.per_kblock + wc.per_tile) +
+                          wc.split_const + wc.per_split * split;
+      if (cost < best.cost || forced_split > 1) best = Candidate{bn, pair, split, 0, cost};
+    }
+  } else if (tiles > units && (tiles % units) != 0) {
+    // split-K tail
+    const int tail = tiles % units;
+    const int split = forced_split > 1 ? forced_split : cap_split(units / tail);
+    if (split > 1 && (tail * split <= units || forced_split > 1) && tail * per_unit <= kMaxCounters) {
+      const double cost = (tiles / units) * (kblocks * wc.per_kblock + wc.per_tile) +
+                          ceil_div(tail * split, units) * (ceil_div(kblocks, split) * wc.per_kblock + wc.per_tile) +
+                          wc.split_const + wc.per_split * split;
+      if (cost < best.cost || forced_split > 1) best = Candidate{bn, pair, split, tiles - tail, cost};
     }
   }
-  const WidthCost wc = width_cost(bn);
-  const int waves = ceil_div(tiles * split, units);
-  double cost = waves * (ceil_div(kblocks, split) * wc.per_kblock + wc.per_tile);
-  if (split > 1) cost += wc.split_const + wc.per_split * split;
-  if (pair) cost *= 1.04;  // measured: a few percent slower than single CTAs in short runs
-  return Candidate{bn, pair, split, cost};
+  if (pair) best.cost *= 1.04;  // measured: a few percent slower than single CTAs in short runs
+  return best;
 }
 
 void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forced, b200_fp8_mm_plan* out) {
@@ -1049,7 +1071,7 @@ void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forc
   const int f_bn = (forced && forced->block_n) ? forced->block_n : 0;
   const int f_pair = (forced && forced->cta_pair) ? (forced->cta_pair > 0 ? 1 : 0) : -1;  // -1: choose
   const int f_split = (forced && forced->split_k) ? forced->split_k : 0;
-  Candidate best{0, 0, 1, 1e300};
+  Candidate best{0, 0, 1, 0, 1e300};
   const int cands[4] = {256, 192, 128, 64};
   for (int pair = 1; pair >= 0; --pair) {
     if (f_pair >= 0 && pair != f_pair) continue;
@@ -1060,15 +1082,16 @@ void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forc
       if (c.cost < best.cost - 1e-9) best = c;
     }
   }
-  if (best.bn == 0) best = Candidate{f_bn, f_pair > 0 ? 1 : 0, f_split ? f_split : 1, 0.0};  // invalid forced width
+  if (best.bn == 0) best = Candidate{f_bn, f_pair > 0 ? 1 : 0, 1, 0, 0.0};  // invalid forced width
   const int pair = best.pair;
   const int bn = best.bn;
   const int tiles = ceil_div(M, pair ? 2 * kBlockM : kBlockM) * ceil_div(N, bn > 0 ? bn : 1);
   const int units = pair ? sm_count / 2 : sm_count;
+  const int full_tiles = best.split > 1 ? best.full_tiles : tiles;
   int store_bufs = (forced && forced->store_bufs) ? (forced->store_bufs > 0 ? forced->store_bufs : 0) : -1;
   if (store_bufs < 0)
-    store_bufs = (best.split > 1 || !valid_block_n(bn)) ? 0 : store_bufs_for(bn, pair, ceil_div(kblocks, best.split));
-  if (best.split > 1) store_bufs = 0;  // split-K tiles leave through the fp32 planes
+    store_bufs = (full_tiles == 0 || !valid_block_n(bn)) ? 0 : store_bufs_for(bn, pair, kblocks);
+  if (full_tiles == 0 && best.split > 1) store_bufs = 0;  // every tile leaves through the fp32 planes first
   const int stages =
       (forced && forced->stages) ? forced->stages : (valid_block_n(bn) ? max_stages_for(bn, pair, store_bufs) : 2);
   out->block_m = kBlockM;
@@ -1077,7 +1100,8 @@ void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forc
   out->split_k = best.split;
   out->stages = stages;
   out->tiles = tiles;
-  const int work = tiles * best.split;
+  out->full_tiles = full_tiles;
+  const int work = full_tiles + (tiles - full_tiles) * best.split;
   const int used = work < units ? work : units;
   out->grid = pair ? 2 * used : used;
   out->store_bufs = store_bufs;
@@ -1091,7 +1115,8 @@ bool plan_is_supported(const b200_fp8_mm_plan& pl, int kblocks) {
   if (pl.store_bufs < 0 || pl.store_bufs > 2) return false;
   if (pl.smem_bytes > kMaxSmem) return false;
   if (pl.split_k < 1 || pl.split_k > kblocks) return false;
-  if (pl.split_k > 1 && pl.tiles * (pl.cta_pair ? 2 : 1) > kMaxCounters) return false;
+  if (pl.split_k > 1 && (pl.tiles - pl.full_tiles) * (pl.cta_pair ? 2 : 1) > kMaxCounters) return false;
+  if (pl.full_tiles < 0 || pl.full_tiles > pl.tiles) return false;
   return true;
 }
 
@@ -1182,6 +1207,7 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   kp.tiles_m = ceil_div(M, pl.cta_pair ? 2 * kBlockM : kBlockM);
   kp.tiles_n = ceil_div(N, pl.block_n);
   kp.split_k = pl.split_k;
+  kp.full_tiles = pl.full_tiles;
   kp.kblocks = kblocks;
   kp.stages = pl.stages;
   kp.tmem_bufs = tmem_bufs_in_use(pl.block_n, pl.stages);
@@ -1365,6 +1391,6 @@ const char* b200_fp8_mm_strerror(int code) {
   }
 }
 
-int b200_fp8_mm_abi_version(void) { return 2; }
+int b200_fp8_mm_abi_version(void) { return 3; }
 
 }  // extern "C"

@@ -25,15 +25,16 @@ class Plan:
     tiles: int = 0
     smem_bytes: int = 0
     store_bufs: int = 0
+    full_tiles: int = 0
 
     def to_c(self) -> _lib.CPlan:
         return _lib.CPlan(self.block_m, self.block_n, self.cta_pair, self.split_k, self.stages, self.grid,
-                          self.tiles, self.smem_bytes, self.store_bufs)
+                          self.tiles, self.smem_bytes, self.store_bufs, self.full_tiles)
 
     @staticmethod
     def from_c(c: _lib.CPlan) -> "Plan":
         return Plan(c.block_m, c.block_n, c.cta_pair, c.split_k, c.stages, c.grid, c.tiles, c.smem_bytes,
-                    c.store_bufs)
+                    c.store_bufs, c.full_tiles)
 
 
 class Fp8MmError(RuntimeError):

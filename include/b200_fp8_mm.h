@@ -57,13 +57,16 @@ typedef struct b200_fp8_mm_plan {
   int block_m;    /* rows of C per CTA (128)                                        */
   int block_n;    /* columns of C per tile: 64, 128, 192 or 256                     */
   int cta_pair;   /* 1: two CTAs share a 256-row tile through cta_group::2          */
-  int split_k;    /* number of K ranges per tile (1 = no split)                     */
+  int split_k;    /* number of K ranges per split tile (1 = no tile is split)       */
   int stages;     /* depth of the TMA -> shared memory ring                         */
   int grid;       /* CTAs launched (persistent; a multiple of 2 when cta_pair)      */
   int tiles;      /* output tiles (x split_k = work items)                          */
   int smem_bytes; /* dynamic shared memory per CTA                                  */
   int store_bufs; /* staging buffers per warpgroup for the TMA store of c: 1 or 2;
-                     0 = plain stores (split-K plans, or forced with -1)             */
+                     0 = plain stores (every tile split, or forced with -1)          */
+  int full_tiles; /* output: tiles [0, full_tiles) run whole, the rest (the tail of a
+                     partly filled last wave, or all tiles when there are few) are
+                     split split_k ways along K                                     */
 } b200_fp8_mm_plan;
 
 /*

@@ -70,14 +70,16 @@ def test_selector_is_pure_and_sane(built_library):
         assert p1.block_m == 128 and p1.block_n in (64, 128, 192, 256)
         assert 1 <= p1.split_k <= k // 128
         assert 2 <= p1.stages <= 8 and p1.smem_bytes <= 232448
-        assert p1.store_bufs in (0, 1, 2) and (p1.store_bufs == 0) == (p1.split_k > 1)
+        assert p1.store_bufs in (0, 1, 2) and 0 <= p1.full_tiles <= p1.tiles
+        assert (p1.full_tiles == p1.tiles) == (p1.split_k == 1)
+        assert (p1.store_bufs == 0) == (p1.full_tiles == 0)
         tiles = -(-m // (p1.block_m * (2 if p1.cta_pair else 1))) * -(-n // p1.block_n)
         assert p1.tiles == tiles
         assert 1 <= p1.grid <= 148 and p1.grid <= tiles * p1.split_k * (2 if p1.cta_pair else 1)
         ws = pkg.workspace_bytes(m, n, k)
         assert (ws == 0) == (p1.split_k == 1)
         if p1.split_k > 1:
-            assert ws >= 4096 + p1.tiles * p1.split_k * 128 * p1.block_n * 4
+            assert ws >= 4096 + (p1.tiles - p1.full_tiles) * p1.split_k * 128 * p1.block_n * 4
     with pytest.raises(Exception):
         pkg.describe(128, 128, 100)
 

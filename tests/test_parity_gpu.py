@@ -129,6 +129,23 @@ def test_every_kernel_variant(plan):
     assert_close(c, ref, str(plan) + " stages=2")
 
 
+@pytest.mark.parametrize("bn,split", [(192, 2), (128, 3), (64, 2)])
+def test_split_k_tail_of_a_partly_filled_last_wave(bn, split):
+    """More tiles than SMs, not a whole number of waves: the full waves run whole tiles, the tail is
+    split along K (whole and split tiles in one launch)."""
+    m, n, k = 4096, 2304, 1024
+    plan_probe = pkg.describe(m, n, k)
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, 17)
+    c.fill_(float("nan"))
+    plan = Plan(block_n=bn, cta_pair=-1, split_k=split)
+    run(a, b, a_s, b_s, c, plan=plan)
+    assert plan_probe.tiles > 0
+    assert_close(c, oracle.dequant_matmul(a, b, a_s, b_s), f"tail bn={bn} split={split}")
+    c2 = torch.full_like(c, float("nan"))
+    run(a, b, a_s, b_s, c2, plan=plan)
+    assert torch.equal(c2.view(torch.int16), c.view(torch.int16))
+
+
 def test_split_k_is_deterministic_and_leaves_counters_clean():
     m, n, k = 256, 1536, 7168
     a, b, a_s, b_s, c = cuda_inputs(m, n, k, 5)
