@@ -34,6 +34,9 @@ UNIT = "TFLOP/s"
 NOMINAL_FP8_TFLOPS = 4500.0
 FALLBACK_BF16_TFLOPS = 1590.0
 L2_BYTES = 126 * 1024 * 1024
+# DRAM bytes of one launch of the headline GEMM on one GPU, from the ncu capture summarised in
+# profiles/fp8_mm_blockscaled_kernel_192_headline_ncu_full.md (108.7 MB read + 61.2 MB written).
+HEADLINE_DRAM_BYTES = 169_900_000
 SWEEP_NK = ((1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
             (512, 7168), (4096, 512))
 SWEEP_M = (512, 2048, 8192, 16384)
@@ -351,7 +354,9 @@ def run_ours(args):
             "roofline": {"bound": "tensor", "achieved": round(per_gpu_tflops, 2), "peak": round(fp8_peak, 1),
                          "unit": "TFLOP/s", "frac": round(per_gpu_tflops / fp8_peak, 4),
                          "peak_source": f"2 x bf16_tflops of {peaks['source']} (fp8 tcgen05 rate is twice bf16)",
-                         "traffic": None},
+                         "traffic": HEADLINE_DRAM_BYTES if (world == 1 and not args.shape) else None,
+                         "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)",
+                         "algorithmic_bytes": algorithmic_bytes(m, n_loc, k)},
             "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 3), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps,
