@@ -10,12 +10,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # B200_FP8_MM_LIB selects another build of the same library (e.g. one made with extra nvcc flags).
 LIB_PATH = os.environ.get("B200_FP8_MM_LIB") or os.path.join(HERE, "lib", "libb200fp8mm.so")
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 # Every symbol include/b200_fp8_mm.h declares.
 EXPORTS = (
     "b200_fp8_mm",
     "b200_fp8_mm_planned",
+    "b200_fp8_mm_strided",
     "b200_fp8_mm_static_scratch",
     "b200_fp8_mm_static_scratch_limit",
     "b200_fp8_mm_workspace_bytes",
@@ -68,6 +69,10 @@ def load() -> ctypes.CDLL:
     lib.b200_fp8_mm.restype = ctypes.c_int
     lib.b200_fp8_mm_planned.argtypes = _GEMM_ARGS + [ctypes.POINTER(CPlan)]
     lib.b200_fp8_mm_planned.restype = ctypes.c_int
+    # both strides of a and b (two more 64-bit integers) and the optional plan
+    lib.b200_fp8_mm_strided.argtypes = (_GEMM_ARGS[:8] + [ctypes.c_longlong] * 9 + _GEMM_ARGS[15:]
+                                        + [ctypes.POINTER(CPlan)])
+    lib.b200_fp8_mm_strided.restype = ctypes.c_int
     # the same argument list without the (workspace, workspace_bytes) pair
     lib.b200_fp8_mm_static_scratch.argtypes = _GEMM_ARGS[:16] + _GEMM_ARGS[18:]
     lib.b200_fp8_mm_static_scratch.restype = ctypes.c_int

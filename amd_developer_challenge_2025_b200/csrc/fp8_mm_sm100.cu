@@ -30,6 +30,9 @@
 // shared-memory operation of a warp (mbarrier probe, ld.shared) takes hundreds of clocks, so
 // the promotion warps touch shared memory as rarely as possible: one barrier wait and one
 // arrive per K block, and the scales of four K blocks fetched with three vector loads.
+// Either operand may also be stored MN-major (a as [K][M], b as [K][N]: the layout the reference's
+// harness hands over). Such a tile is loaded as K rows of 128 (or 64) contiguous M/N bytes and
+// described to the tensor core as an MN-major operand; nothing is transposed in memory.
 // With PAIR, two CTAs of a cluster share one 256-row tile: each loads its own 128 rows of A and
 // half of the B rows, the leader CTA issues tcgen05.mma.cta_group::2 for both, and each CTA
 // promotes and stores its own 128 rows. No TMA load uses cluster multicast.
@@ -79,6 +82,14 @@ struct KernelParams {
   int tmem_bufs;  // TMEM partial buffers in use: divides stages, at most TileCfg::kTmemBufs
   int issuers;     // MMA-issuing threads in use: 1 or 2
   int store_bufs;  // staging buffers per promotion warpgroup for the TMA store of c: 0 (plain stores), 1 or 2
+  // Operand layout, as the values the producer and the MMA threads need (see OperandLayout below).
+  int a_mn, b_mn;            // 1: the operand is MN-major in global and shared memory
+  int b_boxes;               // TMA boxes per stage of b (1 when K-major)
+  int b_box_cols;            // rows of b (columns of c) per box
+  int b_box_bytes;           // shared-memory bytes per box
+  uint32_t a_desc_lo, a_desc_hi, a_kstep;  // descriptor bits beside the address; address step per K=32 MMA
+  uint32_t b_desc_lo, b_desc_hi, b_kstep;
+  uint32_t idesc_major;      // instruction-descriptor bits 15 / 16: a / b is MN-major
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -237,25 +248,25 @@ __device__ __forceinline__ void tcgen05_fence_after() {
 // Descriptors are passed as their 32-bit halves: only the low word (start address) changes from one
 // instruction to the next, which keeps the issuing thread's arithmetic to one add per operand.
 template <bool PAIR>
-__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t a_hi, uint32_t b_hi,
                                         uint32_t idesc, uint32_t accumulate) {
   if constexpr (PAIR) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
         "mov.b64 da, {%1, %3};\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
-        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        "mov.b64 db, {%2, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+        "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   } else {
     asm volatile(
         "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
         "mov.b64 da, {%1, %3};\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
-        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        "mov.b64 db, {%2, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+        "r"(a_lo), "r"(b_lo), "r"(a_hi), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
   }
 }
@@ -370,13 +381,43 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
-// K-major, SWIZZLE_128B shared-memory matrix descriptor (sm_100 format), as two 32-bit words.
-// Low word: start address in 16-byte units (bits 0-13) and the (ignored) leading offset 1 (bit 16).
-// High word: 8-row groups 1024 bytes apart (stride offset 64 in 16-byte units), version 1, layout 2.
-__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) {
-  return ((smem_addr >> 4) & 0x3fffu) | (1u << 16);
+// Shared-memory matrix descriptor (sm_100 format), as two 32-bit words.
+// Low word: start address in 16-byte units (bits 0-13), leading byte offset in 16-byte units (bits 16-29).
+// High word: stride byte offset in 16-byte units (bits 0-13), version 1 (bit 14), swizzle mode (bits 29-31:
+// 2 = 128-byte, 4 = 64-byte).
+// K-major, 128-byte swizzle (a stage row = 128 bytes of K of one matrix row): 8-row groups 1024 bytes apart
+// (stride offset), leading offset unused (1); the next K=32 slice starts 32 bytes further in the row.
+// MN-major (a stage row = 128 or 64 contiguous bytes along M/N of one k): the 8-row groups along K are the
+// stride offset (8 x row pitch), the leading offset is the distance between blocks of 128 (64) M/N values
+// (one TMA box each); the next K=32 slice starts 32 rows further.
+__device__ __forceinline__ uint32_t smem_desc_addr(uint32_t smem_addr) { return (smem_addr >> 4) & 0x3fffu; }
+
+struct OperandLayout {
+  uint32_t desc_lo, desc_hi, kstep;
+  int boxes, box_cols, box_bytes;
+};
+
+// rows = M/N extent of the operand's stage tile (128 for a, block_n for b).
+inline OperandLayout operand_layout(bool mn_major, int rows) {
+  OperandLayout L;
+  if (!mn_major) {
+    L.desc_lo = 1u << 16;
+    L.desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    L.kstep = 32u >> 4;
+    L.boxes = 1;
+    L.box_cols = rows;
+    L.box_bytes = rows * kBlockK;
+    return L;
+  }
+  const int span = (rows % 128 == 0) ? 128 : 64;  // bytes of M/N per shared-memory row = swizzle span
+  L.boxes = rows / span;
+  L.box_cols = span;
+  L.box_bytes = span * kBlockK;                   // 128 k-rows
+  L.desc_lo = static_cast<uint32_t>(L.box_bytes >> 4) << 16;
+  L.desc_hi = static_cast<uint32_t>((8 * span) >> 4) | (1u << 14) | ((span == 128 ? 2u : 4u) << 29);
+  L.kstep = static_cast<uint32_t>((32 * span) >> 4);
+  return L;
 }
-constexpr uint32_t kSmemDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
 
 // kind::f8f6f4 instruction descriptor: D = fp32, A = B = e4m3, both K-major, M x N as given.
 __host__ __device__ constexpr uint32_t make_idesc(int umma_m, int umma_n) {
@@ -548,8 +589,19 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             const uint32_t fb = PAIR ? map_to_cta(smem_u32(&full_bar[stage]), 0) : smem_u32(&full_bar[stage]);
             mbar_expect_tx_cluster(fb, Cfg::kStageBytes);
             const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
-            tma_load_2d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, fb);
-            tma_load_2d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, fb);
+            // K-major: x = byte of K, y = matrix row. MN-major: x = matrix row (a multiple of 64), y = k.
+            if (!p.a_mn) {
+              tma_load_2d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, fb);
+            } else {
+              tma_load_2d<PAIR>(sa, &tmap_a, a_row, kb * kBlockK, fb);
+            }
+            if (!p.b_mn) {
+              tma_load_2d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, fb);
+            } else {
+              for (int i = 0; i < p.b_boxes; ++i)
+                tma_load_2d<PAIR>(sa + Cfg::kStageBytesA + static_cast<uint32_t>(i * p.b_box_bytes), &tmap_b,
+                                  b_row + i * p.b_box_cols, kb * kBlockK, fb);
+            }
             if (++stage == stages) {
               stage = 0;
               phase ^= 1u;
@@ -565,7 +617,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       // about 700 clocks per K block on its barrier wait and on issuing (an MMA costs the issuing
       // thread roughly 100 clocks), more than the tensor pipe needs for a narrow tile's block.
       if (lane == 0 && cta_rank == 0 && warp - 1 < p.issuers) {
-        constexpr uint32_t idesc = make_idesc(Cfg::kTileM, BN);
+        const uint32_t idesc = make_idesc(Cfg::kTileM, BN) | p.idesc_major;
+        const uint32_t a_hi = p.a_desc_hi, b_hi = p.b_desc_hi, a_kstep = p.a_kstep, b_kstep = p.b_kstep;
         const int me = warp - 1;
         // Both issuers walk every K block and keep the ring position with increments only (no
         // division on this thread: its scalar work is on the critical path); each issues for the
@@ -587,8 +640,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             if (++buf == nbufs) buf = 0;
             if (!mine) continue;
             const uint32_t sa = smem_u32(smem + my_stage * Cfg::kStageBytes);
-            const uint32_t a_lo = smem_desc_lo(sa);
-            const uint32_t b_lo = smem_desc_lo(sa + Cfg::kStageBytesA);
+            const uint32_t a_lo = smem_desc_addr(sa) | p.a_desc_lo;
+            const uint32_t b_lo = smem_desc_addr(sa + Cfg::kStageBytesA) | p.b_desc_lo;
             const uint32_t d_addr = tmem_base + static_cast<uint32_t>(my_buf * BN);
             // operands landed AND the TMEM buffer of this K block drained (see the promotion warps)
             if (!mbar_wait(smem_u32(&full_bar[my_stage]), my_phase, ctx, 0x300 | my_stage)) {
@@ -598,8 +651,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             tcgen05_fence_after();
 #pragma unroll
             for (int k = 0; k < kMmasPerBlock; ++k) {
-              // 32 bytes further along K inside the 128-byte swizzle row = +2 in 16-byte units
-              umma_f8<PAIR>(d_addr, a_lo + 2u * k, b_lo + 2u * k, kSmemDescHi, idesc, k > 0 ? 1u : 0u);
+              // next K=32 slice: 32 bytes further inside the swizzle row (K-major) or 32 rows further
+              umma_f8<PAIR>(d_addr, a_lo + a_kstep * k, b_lo + b_kstep * k, a_hi, b_hi, idesc, k > 0 ? 1u : 0u);
             }
             umma_commit<PAIR>(smem_u32(&done_bar[my_stage]));
           }
@@ -918,17 +971,24 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// e4m3 matrix [rows, K] with K contiguous, box = 128 bytes of K x box_rows rows, 128-byte swizzle.
-bool encode_operand_map(CUtensorMap* map, const void* base, int rows, int K, long long ld, int box_rows) {
+// e4m3 matrix of `rows` rows (M or N) and K columns. K-major (K contiguous, row pitch ld): box = 128 bytes of
+// K x box_rows rows, 128-byte swizzle. MN-major (rows contiguous, ld bytes between consecutive k): box =
+// box_rows (128 or 64) bytes of rows x 128 k, swizzle span = the box's inner extent.
+bool encode_operand_map(CUtensorMap* map, const void* base, int rows, int K, long long ld, int box_rows,
+                        bool mn_major) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn_major ? rows : K),
+                              static_cast<cuuint64_t>(mn_major ? K : rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(mn_major ? box_rows : kBlockK),
+                             static_cast<cuuint32_t>(mn_major ? kBlockK : box_rows)};
   const cuuint32_t elem_strides[2] = {1, 1};
+  const CUtensorMapSwizzle swz =
+      (mn_major && box_rows == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
@@ -1147,14 +1207,33 @@ int device_sm_count() {
   return cached[dev];
 }
 
+// Storage of one fp8 operand from its two element strides: K-major (k stride 1) or MN-major (row stride 1).
+// Returns false when it is neither, or when the pitch is one the TMA unit cannot address.
+bool classify_operand(long long s_row, long long s_k, int rows, int K, bool* mn_major, long long* ld) {
+  if (s_k == 1 && s_row >= K) {
+    *mn_major = false;
+    *ld = s_row;
+  } else if (s_row == 1 && s_k >= rows) {
+    *mn_major = true;
+    *ld = s_k;
+  } else {
+    return false;
+  }
+  return (*ld % 16) == 0;
+}
+
 int run(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int M, int N, int K,
-        long long lda, long long ldb, long long sa_m, long long sa_k, long long sb_n, long long sb_k, long long ldc,
-        int n_phase, void* workspace, size_t workspace_bytes, int* device_status, void* stream,
-        const b200_fp8_mm_plan* forced) {
+        long long a_sm, long long a_sk, long long b_sn, long long b_sk, long long sa_m, long long sa_k,
+        long long sb_n, long long sb_k, long long ldc, int n_phase, void* workspace, size_t workspace_bytes,
+        int* device_status, void* stream, const b200_fp8_mm_plan* forced_in) {
   if (a == nullptr || b == nullptr || a_scale == nullptr || b_scale == nullptr || c == nullptr)
     return B200_FP8_MM_ERR_NULL;
   if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return B200_FP8_MM_ERR_SHAPE;
-  if (lda < K || ldb < K || (lda % 16) != 0 || (ldb % 16) != 0 || ldc < N) return B200_FP8_MM_ERR_STRIDE;
+  bool a_mn = false, b_mn = false;
+  long long lda = 0, ldb = 0;
+  if (!classify_operand(a_sm, a_sk, M, K, &a_mn, &lda) || !classify_operand(b_sn, b_sk, N, K, &b_mn, &ldb) ||
+      ldc < N)
+    return B200_FP8_MM_ERR_STRIDE;
   if ((reinterpret_cast<uintptr_t>(a) % 16) != 0 || (reinterpret_cast<uintptr_t>(b) % 16) != 0)
     return B200_FP8_MM_ERR_ALIGN;
   if (n_phase < 0 || n_phase >= 128 || (n_phase % 32) != 0) return B200_FP8_MM_ERR_PHASE;
@@ -1162,6 +1241,19 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   const int sm_count = device_sm_count();
   if (sm_count <= 0) return B200_FP8_MM_ERR_DRIVER;
 
+  // CTA pairs exist for K-major operands only.
+  b200_fp8_mm_plan forced_copy;
+  const b200_fp8_mm_plan* forced = forced_in;
+  if (a_mn || b_mn) {
+    if (forced_in != nullptr && forced_in->cta_pair > 0) return B200_FP8_MM_ERR_PLAN;
+    if (forced_in != nullptr) {
+      forced_copy = *forced_in;
+    } else {
+      memset(&forced_copy, 0, sizeof(forced_copy));
+    }
+    forced_copy.cta_pair = -1;
+    forced = &forced_copy;
+  }
   b200_fp8_mm_plan pl;
   choose_plan(M, N, K, sm_count, forced, &pl);
   const int kblocks = K / kBlockK;
@@ -1183,9 +1275,10 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   } else {
     memset(&map_c, 0, sizeof(map_c));
   }
-  if (!encode_operand_map(&map_a, a, M, K, lda, kBlockM)) return B200_FP8_MM_ERR_DRIVER;
-  if (!encode_operand_map(&map_b, b, N, K, ldb, pl.cta_pair ? pl.block_n / 2 : pl.block_n))
-    return B200_FP8_MM_ERR_DRIVER;
+  const OperandLayout la = operand_layout(a_mn, kBlockM);
+  const OperandLayout lb = operand_layout(b_mn, pl.cta_pair ? pl.block_n / 2 : pl.block_n);
+  if (!encode_operand_map(&map_a, a, M, K, lda, la.box_cols, a_mn)) return B200_FP8_MM_ERR_DRIVER;
+  if (!encode_operand_map(&map_b, b, N, K, ldb, lb.box_cols, b_mn)) return B200_FP8_MM_ERR_DRIVER;
 
   KernelParams kp;
   memset(&kp, 0, sizeof(kp));
@@ -1212,6 +1305,18 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   kp.stages = pl.stages;
   kp.tmem_bufs = tmem_bufs_in_use(pl.block_n, pl.stages);
   kp.store_bufs = store_bufs;
+  kp.a_mn = a_mn ? 1 : 0;
+  kp.b_mn = b_mn ? 1 : 0;
+  kp.b_boxes = lb.boxes;
+  kp.b_box_cols = lb.box_cols;
+  kp.b_box_bytes = lb.box_bytes;
+  kp.a_desc_lo = la.desc_lo;
+  kp.a_desc_hi = la.desc_hi;
+  kp.a_kstep = la.kstep;
+  kp.b_desc_lo = lb.desc_lo;
+  kp.b_desc_hi = lb.desc_hi;
+  kp.b_kstep = lb.kstep;
+  kp.idesc_major = (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u);
   // Two issuing threads pay off where the MMAs are short (narrow tiles: 25 % faster at block_n 64,
   // 10 % at 128); the wide tiles are bound by the promotion warps and run 1 % better with one.
   kp.issuers = pl.block_n <= 128 ? 2 : 1;
@@ -1308,15 +1413,23 @@ int b200_fp8_mm(const void* a, const void* b, const float* a_scale, const float*
                 int K, long long lda, long long ldb, long long sa_m, long long sa_k, long long sb_n, long long sb_k,
                 long long ldc, int n_phase, void* workspace, size_t workspace_bytes, int* device_status,
                 void* stream) {
-  return run(a, b, a_scale, b_scale, c, M, N, K, lda, ldb, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, workspace,
+  return run(a, b, a_scale, b_scale, c, M, N, K, lda, 1, ldb, 1, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, workspace,
              workspace_bytes, device_status, stream, nullptr);
+}
+
+int b200_fp8_mm_strided(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int M,
+                        int N, int K, long long a_sm, long long a_sk, long long b_sn, long long b_sk, long long sa_m,
+                        long long sa_k, long long sb_n, long long sb_k, long long ldc, int n_phase, void* workspace,
+                        size_t workspace_bytes, int* device_status, void* stream, const b200_fp8_mm_plan* forced) {
+  return run(a, b, a_scale, b_scale, c, M, N, K, a_sm, a_sk, b_sn, b_sk, sa_m, sa_k, sb_n, sb_k, ldc, n_phase,
+             workspace, workspace_bytes, device_status, stream, forced);
 }
 
 int b200_fp8_mm_planned(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int M,
                         int N, int K, long long lda, long long ldb, long long sa_m, long long sa_k, long long sb_n,
                         long long sb_k, long long ldc, int n_phase, void* workspace, size_t workspace_bytes,
                         int* device_status, void* stream, const b200_fp8_mm_plan* forced) {
-  return run(a, b, a_scale, b_scale, c, M, N, K, lda, ldb, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, workspace,
+  return run(a, b, a_scale, b_scale, c, M, N, K, lda, 1, ldb, 1, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, workspace,
              workspace_bytes, device_status, stream, forced);
 }
 
@@ -1342,7 +1455,7 @@ int b200_fp8_mm_static_scratch(const void* a, const void* b, const float* a_scal
       return B200_FP8_MM_ERR_LAUNCH;
     }
   }
-  return run(a, b, a_scale, b_scale, c, M, N, K, lda, ldb, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, scratch,
+  return run(a, b, a_scale, b_scale, c, M, N, K, lda, 1, ldb, 1, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, scratch,
              kStaticScratchBytes, device_status, stream, nullptr);
 }
 
@@ -1350,9 +1463,15 @@ size_t b200_fp8_mm_static_scratch_limit(void) { return kStaticScratchBytes; }
 
 size_t b200_fp8_mm_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return 0;
-  b200_fp8_mm_plan pl;
+  // Covers both the plan for K-major operands and the one for MN-major operands (no CTA pairs).
+  b200_fp8_mm_plan pl, single;
   choose_plan(M, N, K, 148, nullptr, &pl);
-  const size_t need = plan_workspace_bytes(pl);
+  memset(&single, 0, sizeof(single));
+  single.cta_pair = -1;
+  b200_fp8_mm_plan pl2;
+  choose_plan(M, N, K, 148, &single, &pl2);
+  size_t need = plan_workspace_bytes(pl);
+  if (plan_workspace_bytes(pl2) > need) need = plan_workspace_bytes(pl2);
   return ((need + 255) / 256) * 256;
 }
 
@@ -1377,7 +1496,8 @@ const char* b200_fp8_mm_strerror(int code) {
     case B200_FP8_MM_OK: return "ok";
     case B200_FP8_MM_ERR_NULL: return "a required pointer is NULL";
     case B200_FP8_MM_ERR_SHAPE: return "bad shape: M, N, K must be positive and K a multiple of 128";
-    case B200_FP8_MM_ERR_STRIDE: return "unsupported stride: a and b need K contiguous, row strides multiples of 16";
+    case B200_FP8_MM_ERR_STRIDE:
+      return "unsupported stride: a and b need either K or M/N contiguous and a pitch that is a multiple of 16";
     case B200_FP8_MM_ERR_ALIGN: return "a and b must be 16-byte aligned";
     case B200_FP8_MM_ERR_PHASE: return "n_phase must be 0, 32, 64 or 96";
     case B200_FP8_MM_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
@@ -1391,6 +1511,6 @@ const char* b200_fp8_mm_strerror(int code) {
   }
 }
 
-int b200_fp8_mm_abi_version(void) { return 3; }
+int b200_fp8_mm_abi_version(void) { return 4; }
 
 }  // extern "C"

@@ -5,7 +5,7 @@ Mirrors the reference's pybind launcher `fp8_mm(a, b, as, bs, c, c_tmp)`
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 
 import torch
 
@@ -118,18 +118,30 @@ def _validate(a, b, a_scale, b_scale, c, n_phase, plan):
     nb = (n + n_phase + SCALE_BLOCK - 1) // SCALE_BLOCK
     _check(tuple(a_scale.shape) == (m, kb), f"a_scale must be [{m}, {kb}]")
     _check(tuple(b_scale.shape) == (nb, kb), f"b_scale must be [{nb}, {kb}]")
-    _check(a.stride(1) == 1 and b.stride(1) == 1,
-           "a and b must have K contiguous (M-major/N-major storage is not supported yet)")
+    mn_major = False
+    for name, t, rows in (("a", a, m), ("b", b, n)):
+        k_major = t.stride(1) == 1 and t.stride(0) >= k
+        mn = t.stride(0) == 1 and t.stride(1) >= rows
+        _check(k_major or mn, f"{name} must have either K contiguous or its {'M' if name == 'a' else 'N'} "
+                              "dimension contiguous")
+        pitch = t.stride(0) if k_major else t.stride(1)
+        _check(pitch % 16 == 0 and t.data_ptr() % 16 == 0, f"{name}: pitch and base address must be multiples of 16")
+        mn_major = mn_major or not k_major
     _check(c.stride(1) == 1, "c must have N contiguous")
     dev = a.device
     _check(all(t.device == dev for t in (b, a_scale, b_scale, c)), "tensors on different devices")
+    if plan is not None and mn_major:
+        _check(plan.cta_pair <= 0, "CTA pairs need K-major a and b")
+        plan = replace(plan, cta_pair=-1)  # the plan the library sizes the workspace for
     return workspace_bytes(m, n, k, plan), (plan.to_c() if plan is not None else None)
 
 
 def fp8_mm(a, b, a_scale, b_scale, c, n_phase: int = 0, plan: Plan | None = None, check: bool = False):
     """c[M,N] (bf16) = block-scaled a[M,K] @ b[N,K]^T on the current CUDA stream; returns c.
 
-    a, b: float8_e4m3fn with K contiguous. a_scale: fp32 [M, K/128], any strides.
+    a [M,K], b [N,K]: float8_e4m3fn, each either with K contiguous or with its M / N dimension
+    contiguous (the `[K][M]` storage the reference's harness hands over, e.g. `x.t().contiguous().t()`);
+    the other stride a multiple of 16. a_scale: fp32 [M, K/128], any strides.
     b_scale: fp32 [ceil((N+n_phase)/128), K/128], any strides. `n_phase`: offset of b's first
     row inside its 128-row scale block (0 unless b is a column shard of a larger matrix).
     `plan`: force tile parameters (sweeps/tests). `check`: synchronise and raise if a wait
@@ -158,14 +170,11 @@ def fp8_mm(a, b, a_scale, b_scale, c, n_phase: int = 0, plan: Plan | None = None
     args = (
         a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), c.data_ptr(),
         m, n, k,
-        sa[0], sb[0], sas[0], sas[1], sbs[0], sbs[1], sc[0], n_phase,
+        sa[0], sa[1], sb[0], sb[1], sas[0], sas[1], sbs[0], sbs[1], sc[0], n_phase,
         ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
         st.data_ptr(), stream,
     )
-    if cplan is None:
-        rc = lib.b200_fp8_mm(*args)
-    else:
-        rc = lib.b200_fp8_mm_planned(*args, ctypes.byref(cplan))
+    rc = lib.b200_fp8_mm_strided(*args, ctypes.byref(cplan) if cplan is not None else None)
     if rc != 0:
         raise Fp8MmError(rc, f"M={m} N={n} K={k}")
     if check:

@@ -13,9 +13,16 @@ import torch
 SCALE_BLOCK = 128
 
 
-def make_inputs(m: int, n: int, k: int, seed: int, device: str | torch.device = "cpu"):
+def mn_major(t: torch.Tensor) -> torch.Tensor:
+    """The same [rows, K] matrix stored with `rows` contiguous (stride (1, rows)): the storage the
+    reference's kernels index as `a[k*m + i]` (1-amd-fp8-mm/amd-fp8-mm-submission.py:283-300)."""
+    return t.t().contiguous().t()
+
+
+def make_inputs(m: int, n: int, k: int, seed: int, device: str | torch.device = "cpu", layout: str = "k"):
     """Returns (a, b, a_scale, b_scale, c). Always generated on the CPU from `seed`, so the
-    CPU oracle and the GPU see identical bits, then moved to `device`."""
+    CPU oracle and the GPU see identical bits, then moved to `device`. `layout`: "k" (a and b with
+    K contiguous) or "mn" (both stored MN-major); the values are the same either way."""
     if k % SCALE_BLOCK != 0:
         raise ValueError("K must be a multiple of 128")
     g = torch.Generator(device="cpu").manual_seed(int(seed))
@@ -29,4 +36,8 @@ def make_inputs(m: int, n: int, k: int, seed: int, device: str | torch.device = 
     dev = torch.device(device)
     if dev.type != "cpu":
         a, b, a_scale, b_scale, c = (t.to(dev) for t in (a, b, a_scale, b_scale, c))
+    if layout == "mn":
+        a, b = mn_major(a), mn_major(b)
+    elif layout != "k":
+        raise ValueError("layout must be 'k' or 'mn'")
     return a, b, a_scale, b_scale, c

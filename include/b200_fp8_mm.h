@@ -118,6 +118,34 @@ int b200_fp8_mm_planned(const void* a, const void* b, const float* a_scale, cons
                         const b200_fp8_mm_plan* forced);
 
 /*
+ * The same GEMM with both element strides of a and b given, so that either operand may be
+ * stored MN-major: a as [K][M] (a_sm == 1, a_sk = bytes between consecutive k), b as [K][N]
+ * (b_sn == 1). That is the storage the reference's kernels index (`a[k*m + i]`,
+ * 1-amd-fp8-mm/amd-fp8-mm-submission.py:283-300) and the one its pre-transpose path
+ * rewrites in place before the GEMM (same file, 128-154, 570-571); here the tile is loaded
+ * as it lies and handed to the tensor core as an MN-major operand, nothing is transposed
+ * or written.
+ *
+ *  a   element (i,kk) at a + i*a_sm + kk*a_sk; either a_sk == 1 (K-major, a_sm >= K) or
+ *      a_sm == 1 (MN-major, a_sk >= M); the other stride a multiple of 16
+ *  b   element (j,kk) at b + j*b_sn + kk*b_sk, same rule
+ *  forced  NULL, or a plan as for b200_fp8_mm_planned; CTA pairs are available for
+ *      K-major operands only (cta_pair = 1 with an MN-major operand: B200_FP8_MM_ERR_PLAN)
+ *
+ * Everything else as for b200_fp8_mm. b200_fp8_mm_workspace_bytes covers both layouts.
+ */
+int b200_fp8_mm_strided(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c,
+                        int M, int N, int K,
+                        long long a_sm, long long a_sk,
+                        long long b_sn, long long b_sk,
+                        long long sa_m, long long sa_k,
+                        long long sb_n, long long sb_k,
+                        long long ldc, int n_phase,
+                        void* workspace, size_t workspace_bytes,
+                        int* device_status, void* stream,
+                        const b200_fp8_mm_plan* forced);
+
+/*
  * The same GEMM for callers that cannot allocate device memory. (No counterpart in the
  * reference: its launcher gets its split-K scratch from torch.empty on every call.)
  *
@@ -152,8 +180,8 @@ int b200_fp8_mm_static_scratch(const void* a, const void* b, const float* a_scal
 /* Size in bytes of the scratch array b200_fp8_mm_static_scratch uses. */
 size_t b200_fp8_mm_static_scratch_limit(void);
 
-/* Workspace the plan chosen by b200_fp8_mm for (M,N,K) needs, in bytes (0 when it does
- * not split K). Replaces
+/* Workspace the plan chosen by b200_fp8_mm / b200_fp8_mm_strided for (M,N,K) needs, in bytes
+ * (0 when it does not split K; the larger of the two when the layouts' plans differ). Replaces
  * the reference's per-call `torch.empty(m*n*4)` split-K scratch
  * (1-amd-fp8-mm/amd-fp8-mm-submission.py:597-601). */
 size_t b200_fp8_mm_workspace_bytes(int M, int N, int K);
