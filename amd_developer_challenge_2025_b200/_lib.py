@@ -10,13 +10,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # B200_FP8_MM_LIB selects another build of the same library (e.g. one made with extra nvcc flags).
 LIB_PATH = os.environ.get("B200_FP8_MM_LIB") or os.path.join(HERE, "lib", "libb200fp8mm.so")
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 # Every symbol include/b200_fp8_mm.h declares.
 EXPORTS = (
     "b200_fp8_mm",
     "b200_fp8_mm_planned",
     "b200_fp8_mm_strided",
+    "b200_fp8_mm_grouped",
     "b200_fp8_mm_static_scratch",
     "b200_fp8_mm_static_scratch_limit",
     "b200_fp8_mm_workspace_bytes",
@@ -73,6 +74,9 @@ def load() -> ctypes.CDLL:
     lib.b200_fp8_mm_strided.argtypes = (_GEMM_ARGS[:8] + [ctypes.c_longlong] * 9 + _GEMM_ARGS[15:]
                                         + [ctypes.POINTER(CPlan)])
     lib.b200_fp8_mm_strided.restype = ctypes.c_int
+    lib.b200_fp8_mm_grouped.argtypes = ([ctypes.c_void_p] * 5 + [ctypes.c_int] * 4 + [ctypes.c_longlong] * 12
+                                        + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(CPlan)])
+    lib.b200_fp8_mm_grouped.restype = ctypes.c_int
     # the same argument list without the (workspace, workspace_bytes) pair
     lib.b200_fp8_mm_static_scratch.argtypes = _GEMM_ARGS[:16] + _GEMM_ARGS[18:]
     lib.b200_fp8_mm_static_scratch.restype = ctypes.c_int

@@ -33,6 +33,10 @@
 // Either operand may also be stored MN-major (a as [K][M], b as [K][N]: the layout the reference's
 // harness hands over). Such a tile is loaded as K rows of 128 (or 64) contiguous M/N bytes and
 // described to the tensor core as an MN-major operand; nothing is transposed in memory.
+// Grouped form (one launch for G independent problems of the same N and K, e.g. the experts of an MoE layer):
+// a, b, the scales and c carry a leading group dimension, the work list runs over (group, tile), the tensor
+// maps are three-dimensional, and an optional device array gives the number of valid rows per group
+// (tiles past it are skipped by every role, rows past it are never written).
 // With PAIR, two CTAs of a cluster share one 256-row tile: each loads its own 128 rows of A and
 // half of the B rows, the leader CTA issues tcgen05.mma.cta_group::2 for both, and each CTA
 // promotes and stores its own 128 rows. No TMA load uses cluster multicast.
@@ -90,6 +94,10 @@ struct KernelParams {
   uint32_t a_desc_lo, a_desc_hi, a_kstep;  // descriptor bits beside the address; address step per K=32 MMA
   uint32_t b_desc_lo, b_desc_hi, b_kstep;
   uint32_t idesc_major;      // instruction-descriptor bits 15 / 16: a / b is MN-major
+  // Grouped launches (groups > 0): M, tiles_m, a_scale/b_scale/c strides are per group.
+  int groups;
+  const int* m_valid;        // device int[groups]: rows of each group that exist (null: all M)
+  long long sa_g, sb_g, c_g; // group strides of a_scale, b_scale (floats) and c (elements)
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -209,6 +217,22 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "l"(map), "r"(c0), "r"(c1), "r"(bar)
         : "memory");
   }
+}
+
+// Three-dimensional forms for grouped launches: the third coordinate is the group.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(map), "r"(c0),
+               "r"(c1), "r"(c2), "r"(src)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
 // TMA store of one staged box to c; out-of-range rows and columns are clipped by the hardware.
@@ -460,6 +484,9 @@ struct TileCfg {
 
 struct WorkItem {
   int m0, n0, tile, split, nsplit, kb_begin, kb_end;
+  int group;    // 0 unless grouped
+  int m_limit;  // rows [0, m_limit) of the group exist; a tile with m0 >= m_limit is skipped by every role
+  bool skip;
 };
 
 // Work item w -> tile and K range. Tiles are walked in groups of raster_group tile rows, column
@@ -480,6 +507,14 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
     it.nsplit = p.split_k;
   }
   it.tile = t;
+  it.group = 0;
+  it.m_limit = p.M;
+  if (p.groups > 0) {
+    const int per_problem = p.tiles_m * p.tiles_n;
+    it.group = t / per_problem;
+    t -= it.group * per_problem;
+    if (p.m_valid != nullptr) it.m_limit = max(0, min(p.M, __ldg(p.m_valid + it.group)));
+  }
   const int per_group = p.raster_group * p.tiles_n;
   const int group = t / per_group;
   const int first_m = group * p.raster_group;
@@ -489,6 +524,7 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
   const int tn = within / gsize;
   it.m0 = tm * tile_m;
   it.n0 = tn * block_n;
+  it.skip = it.m0 >= it.m_limit;
   it.kb_begin = static_cast<int>((static_cast<long long>(it.split) * p.kblocks) / it.nsplit);
   it.kb_end = static_cast<int>((static_cast<long long>(it.split + 1) * p.kblocks) / it.nsplit);
   return it;
@@ -564,7 +600,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  const int total_work = p.full_tiles + (p.tiles_m * p.tiles_n - p.full_tiles) * p.split_k;
+  const int all_tiles = p.tiles_m * p.tiles_n * (p.groups > 0 ? p.groups : 1);
+  const int total_work = p.full_tiles + (all_tiles - p.full_tiles) * p.split_k;
   const int work_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int work_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
@@ -578,6 +615,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         bool ok = true;
         for (int w = work_first; w < total_work && ok; w += work_step) {
           const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+          if (it.skip) continue;
           const int a_row = it.m0 + static_cast<int>(cta_rank) * kBlockM;
           const int b_row = it.n0 + static_cast<int>(cta_rank) * (PAIR ? Cfg::kRowsB : 0);
           for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
@@ -590,6 +628,10 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             mbar_expect_tx_cluster(fb, Cfg::kStageBytes);
             const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
             // K-major: x = byte of K, y = matrix row. MN-major: x = matrix row (a multiple of 64), y = k.
+            if (p.groups > 0) {
+              tma_load_3d(sa, &tmap_a, kb * kBlockK, a_row, it.group, fb);
+              tma_load_3d(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
+            } else {
             if (!p.a_mn) {
               tma_load_2d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, fb);
             } else {
@@ -601,6 +643,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               for (int i = 0; i < p.b_boxes; ++i)
                 tma_load_2d<PAIR>(sa + Cfg::kStageBytesA + static_cast<uint32_t>(i * p.b_box_bytes), &tmap_b,
                                   b_row + i * p.b_box_cols, kb * kBlockK, fb);
+            }
             }
             if (++stage == stages) {
               stage = 0;
@@ -628,6 +671,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         bool ok = true;
         for (int w = work_first; w < total_work && ok; w += work_step) {
           const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+          if (it.skip) continue;
           for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
             const bool mine = (turn == me);
             if (++turn == p.issuers) turn = 0;
@@ -668,14 +712,16 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       bool ok = true;
       for (int w = work_first; w < total_work && ok; w += work_step) {
         const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+        if (it.skip) continue;
         const int row0 = it.m0 + static_cast<int>(cta_rank) * kBlockM;
+        const float* a_base = p.a_scale + static_cast<long long>(it.group) * p.sa_g;
         const float* a_src[4];
 #pragma unroll
         for (int r = 0; r < 4; ++r)
-          a_src[r] = p.a_scale + static_cast<long long>(min(row0 + lane + 32 * r, p.M - 1)) * p.sa_m;
+          a_src[r] = a_base + static_cast<long long>(min(row0 + lane + 32 * r, p.M - 1)) * p.sa_m;
         // lanes 0..15: b_scale row (n0 + n_phase)/128 + lane/4 (clamped), K block offset lane%4
         const int jb = min(((it.n0 + p.n_phase) >> 7) + ((lane >> 2) & 3), p.b_scale_rows - 1);
-        const float* b_src = p.b_scale + static_cast<long long>(jb) * p.sb_n;
+        const float* b_src = p.b_scale + static_cast<long long>(it.group) * p.sb_g + static_cast<long long>(jb) * p.sb_n;
         for (int kb = it.kb_begin; kb < it.kb_end; kb += kScaleGroup) {
           if (!mbar_wait(smem_u32(&scale_empty_bar[slot]), sphase ^ 1u, ctx, 0x500 | slot)) {
             ok = false;
@@ -739,6 +785,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 
     for (int w = work_first; w < total_work && ok; w += work_step) {
       const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+      if (it.skip) continue;
       const int row = it.m0 + static_cast<int>(cta_rank) * kBlockM + row_in_tile;
       // Index of this thread's first b_scale row inside a ring slot (at most 2 rows per 128 columns).
       const int gcol0 = it.n0 + col_base + p.n_phase;
@@ -866,7 +913,10 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           }
         }
       }
-      if (do_store && p.store_bufs > 0) {
+      // The TMA store clips at the tensor's edges only: a tile that a group's row count cuts short goes out
+      // through the guarded plain stores instead.
+      const bool tma_rows_ok = (it.m_limit == p.M) || (it.m0 + Cfg::kTileM <= it.m_limit);
+      if (do_store && p.store_bufs > 0 && tma_rows_ok) {
         // bf16 tile -> swizzled staging -> TMA store, 32 columns at a time per warpgroup. The
         // 16-byte piece q of row r sits at r*64 + ((q ^ ((r >> 1) & 3)) * 16) (SWIZZLE_64B), which
         // spreads a warp's stores over all banks.
@@ -898,13 +948,19 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           wg_bar_sync(half);
-          if (wg_tid == 0)
-            tma_store_2d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
-                         it.m0 + static_cast<int>(cta_rank) * kBlockM);
+          if (wg_tid == 0) {
+            if (p.groups > 0) {
+              tma_store_3d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols, it.m0,
+                           it.group);
+            } else {
+              tma_store_2d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
+                           it.m0 + static_cast<int>(cta_rank) * kBlockM);
+            }
+          }
         }
       } else if (do_store) {
-        if (row < p.M) {
-          __nv_bfloat16* crow = p.c + static_cast<long long>(row) * p.ldc;
+        if (row < it.m_limit) {
+          __nv_bfloat16* crow = p.c + static_cast<long long>(it.group) * p.c_g + static_cast<long long>(row) * p.ldc;
 #pragma unroll
           for (int j = 0; j < Cfg::kColsPerThread / 8; ++j) {
             const int col = col0 + j * 8;
@@ -1001,6 +1057,38 @@ bool encode_output_map(CUtensorMap* map, void* base, int M, int N, long long ldc
   const cuuint32_t box[2] = {static_cast<cuuint32_t>(kStoreBoxCols), static_cast<cuuint32_t>(kBlockM)};
   const cuuint32_t elem_strides[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, elem_strides,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Grouped operands: e4m3 [groups][rows][K] with K contiguous, row pitch ld and group pitch lg (bytes);
+// box = 128 bytes of K x box_rows rows of one group.
+bool encode_operand_map_3d(CUtensorMap* map, const void* base, int groups, int rows, int K, long long ld,
+                           long long lg, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(groups)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld), static_cast<cuuint64_t>(lg)};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box,
+                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Grouped output: bf16 [groups][M][N]; rows past M of a group are clipped by the store.
+bool encode_output_map_3d(CUtensorMap* map, void* base, int groups, int M, int N, long long ldc, long long c_g) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M),
+                              static_cast<cuuint64_t>(groups)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ldc) * 2, static_cast<cuuint64_t>(c_g) * 2};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(kStoreBoxCols), static_cast<cuuint32_t>(kBlockM), 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, elem_strides,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -1207,6 +1295,9 @@ int device_sm_count() {
   return cached[dev];
 }
 
+int launch(KernelFn fn, const b200_fp8_mm_plan& pl, const CUtensorMap& map_a, const CUtensorMap& map_b,
+           const CUtensorMap& map_c, const KernelParams& kp, void* stream);
+
 // Storage of one fp8 operand from its two element strides: K-major (k stride 1) or MN-major (row stride 1).
 // Returns false when it is neither, or when the pitch is one the TMA unit cannot address.
 bool classify_operand(long long s_row, long long s_k, int rows, int K, bool* mn_major, long long* ld) {
@@ -1332,6 +1423,11 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   kp.vec_store =
       ((reinterpret_cast<uintptr_t>(c) % 16) == 0 && (ldc % 8) == 0 && (N % 8) == 0) ? 1 : 0;
 
+  return launch(fn, pl, map_a, map_b, map_c, kp, stream);
+}
+
+int launch(KernelFn fn, const b200_fp8_mm_plan& pl, const CUtensorMap& map_a, const CUtensorMap& map_b,
+           const CUtensorMap& map_c, const KernelParams& kp, void* stream) {
   // Opt every kernel in to the full 227 KiB of dynamic shared memory once per device.
   cudaError_t err = cudaSuccess;
   {
@@ -1370,6 +1466,105 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
     return B200_FP8_MM_ERR_LAUNCH;
   }
   return B200_FP8_MM_OK;
+}
+
+// Grouped launch: `groups` problems of the same N and K in one kernel. Every tile is a whole tile (no
+// split-K, no CTA pairs); the tile width is chosen as for one GEMM with all groups' row blocks stacked.
+int run_grouped(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int groups, int M,
+                int N, int K, long long lda, long long a_g, long long ldb, long long b_g, long long sa_g,
+                long long sa_m, long long sa_k, long long sb_g, long long sb_n, long long sb_k, long long ldc,
+                long long c_g, const int* m_valid, int* device_status, void* stream,
+                const b200_fp8_mm_plan* forced_in) {
+  if (a == nullptr || b == nullptr || a_scale == nullptr || b_scale == nullptr || c == nullptr)
+    return B200_FP8_MM_ERR_NULL;
+  if (groups <= 0 || M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return B200_FP8_MM_ERR_SHAPE;
+  const int tiles_m = ceil_div(M, kBlockM);
+  if (static_cast<long long>(groups) * tiles_m > (1 << 20)) return B200_FP8_MM_ERR_SHAPE;
+  if (lda < K || ldb < K || (lda % 16) != 0 || (ldb % 16) != 0 || ldc < N || (a_g % 16) != 0 || (b_g % 16) != 0 ||
+      a_g < lda || b_g < ldb || c_g < ldc)
+    return B200_FP8_MM_ERR_STRIDE;
+  if ((reinterpret_cast<uintptr_t>(a) % 16) != 0 || (reinterpret_cast<uintptr_t>(b) % 16) != 0)
+    return B200_FP8_MM_ERR_ALIGN;
+  const int sm_count = device_sm_count();
+  if (sm_count <= 0) return B200_FP8_MM_ERR_DRIVER;
+
+  b200_fp8_mm_plan forced;
+  if (forced_in != nullptr) {
+    if (forced_in->cta_pair > 0 || forced_in->split_k > 1) return B200_FP8_MM_ERR_PLAN;
+    forced = *forced_in;
+  } else {
+    memset(&forced, 0, sizeof(forced));
+  }
+  forced.cta_pair = -1;
+  forced.split_k = 1;
+  b200_fp8_mm_plan pl;
+  choose_plan(groups * tiles_m * kBlockM, N, K, sm_count, &forced, &pl);
+  if (!plan_is_supported(pl, K / kBlockK) || pl.split_k != 1 || pl.cta_pair != 0) return B200_FP8_MM_ERR_PLAN;
+  KernelFn fn = kernel_for(pl.block_n, 0);
+  if (fn == nullptr) return B200_FP8_MM_ERR_PLAN;
+
+  CUtensorMap map_a, map_b, map_c;
+  int store_bufs = pl.store_bufs;
+  if ((reinterpret_cast<uintptr_t>(c) % 16) != 0 || (ldc % 8) != 0 || (c_g % 8) != 0) store_bufs = 0;
+  if (store_bufs > 0) {
+    if (!encode_output_map_3d(&map_c, c, groups, M, N, ldc, c_g)) return B200_FP8_MM_ERR_DRIVER;
+  } else {
+    memset(&map_c, 0, sizeof(map_c));
+  }
+  if (!encode_operand_map_3d(&map_a, a, groups, M, K, lda, a_g, kBlockM)) return B200_FP8_MM_ERR_DRIVER;
+  if (!encode_operand_map_3d(&map_b, b, groups, N, K, ldb, b_g, pl.block_n)) return B200_FP8_MM_ERR_DRIVER;
+
+  const OperandLayout la = operand_layout(false, kBlockM);
+  const OperandLayout lb = operand_layout(false, pl.block_n);
+  KernelParams kp;
+  memset(&kp, 0, sizeof(kp));
+  kp.a_scale = a_scale;
+  kp.b_scale = b_scale;
+  kp.c = static_cast<__nv_bfloat16*>(c);
+  kp.status = device_status;
+  kp.sa_m = sa_m;
+  kp.sa_k = sa_k;
+  kp.sb_n = sb_n;
+  kp.sb_k = sb_k;
+  kp.ldc = ldc;
+  kp.M = M;
+  kp.N = N;
+  kp.K = K;
+  kp.tiles_m = tiles_m;
+  kp.tiles_n = ceil_div(N, pl.block_n);
+  kp.split_k = 1;
+  kp.full_tiles = groups * kp.tiles_m * kp.tiles_n;
+  kp.kblocks = K / kBlockK;
+  kp.stages = pl.stages;
+  kp.tmem_bufs = tmem_bufs_in_use(pl.block_n, pl.stages);
+  kp.store_bufs = store_bufs;
+  kp.b_boxes = lb.boxes;
+  kp.b_box_cols = lb.box_cols;
+  kp.b_box_bytes = lb.box_bytes;
+  kp.a_desc_lo = la.desc_lo;
+  kp.a_desc_hi = la.desc_hi;
+  kp.a_kstep = la.kstep;
+  kp.b_desc_lo = lb.desc_lo;
+  kp.b_desc_hi = lb.desc_hi;
+  kp.b_kstep = lb.kstep;
+  kp.issuers = pl.block_n <= 128 ? 2 : 1;
+  {
+    int g = (sm_count + kp.tiles_n / 2) / kp.tiles_n;
+    if (g < 1) g = 1;
+    if (g > 16) g = 16;
+    kp.raster_group = g;
+  }
+  kp.b_scale_rows = ceil_div(N, 128);
+  kp.vec_store = ((reinterpret_cast<uintptr_t>(c) % 16) == 0 && (ldc % 8) == 0 && (c_g % 8) == 0 && (N % 8) == 0) ? 1 : 0;
+  kp.groups = groups;
+  kp.m_valid = m_valid;
+  kp.sa_g = sa_g;
+  kp.sb_g = sb_g;
+  kp.c_g = c_g;
+  pl.tiles = kp.full_tiles;
+  pl.full_tiles = kp.full_tiles;
+  pl.grid = kp.full_tiles < sm_count ? kp.full_tiles : sm_count;
+  return launch(fn, pl, map_a, map_b, map_c, kp, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1459,6 +1654,15 @@ int b200_fp8_mm_static_scratch(const void* a, const void* b, const float* a_scal
              kStaticScratchBytes, device_status, stream, nullptr);
 }
 
+int b200_fp8_mm_grouped(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int groups,
+                        int M, int N, int K, long long lda, long long a_g, long long ldb, long long b_g,
+                        long long sa_g, long long sa_m, long long sa_k, long long sb_g, long long sb_n,
+                        long long sb_k, long long ldc, long long c_g, const int* m_valid, int* device_status,
+                        void* stream, const b200_fp8_mm_plan* forced) {
+  return run_grouped(a, b, a_scale, b_scale, c, groups, M, N, K, lda, a_g, ldb, b_g, sa_g, sa_m, sa_k, sb_g, sb_n,
+                     sb_k, ldc, c_g, m_valid, device_status, stream, forced);
+}
+
 size_t b200_fp8_mm_static_scratch_limit(void) { return kStaticScratchBytes; }
 
 size_t b200_fp8_mm_workspace_bytes(int M, int N, int K) {
@@ -1511,6 +1715,6 @@ const char* b200_fp8_mm_strerror(int code) {
   }
 }
 
-int b200_fp8_mm_abi_version(void) { return 4; }
+int b200_fp8_mm_abi_version(void) { return 5; }
 
 }  // extern "C"

@@ -182,6 +182,59 @@ def fp8_mm(a, b, a_scale, b_scale, c, n_phase: int = 0, plan: Plan | None = None
     return c
 
 
+def fp8_mm_grouped(a, b, a_scale, b_scale, c, m_valid=None, plan: Plan | None = None, check: bool = False):
+    """c[g] (bf16 [G,M,N]) = block-scaled a[g] ([G,M,K]) @ b[g]^T ([G,N,K]) for every group g in one launch.
+
+    The FP8 block-scaled form of the per-expert GEMMs the reference's MoE submission runs as fp16
+    `torch.bmm` (2-amd-moe/amd-moe-submission.py:604-611). a_scale: fp32 [G, M, K/128]; b_scale: fp32
+    [G, ceil(N/128), K/128]; any strides for the scales, K contiguous for a and b. `m_valid`: optional
+    int32 CUDA tensor [G]; rows at or past m_valid[g] of group g are neither computed nor written."""
+    lib = _lib.load()
+    _check(all(t.is_cuda for t in (a, b, a_scale, b_scale, c)), "all tensors must be CUDA tensors (there is no CPU path)")
+    _check(a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn, "a and b must be float8_e4m3fn")
+    _check(a_scale.dtype == torch.float32 and b_scale.dtype == torch.float32, "scales must be float32")
+    _check(c.dtype == torch.bfloat16, "c must be bfloat16")
+    _check(a.dim() == 3 and b.dim() == 3 and c.dim() == 3, "a, b, c must be 3-D: [groups, rows, cols]")
+    g, m, k = a.shape
+    n = b.shape[1]
+    _check(b.shape[0] == g and b.shape[2] == k, "a and b disagree on groups or K")
+    _check(tuple(c.shape) == (g, m, n), "c must be [G, M, N]")
+    _check(k % SCALE_BLOCK == 0, "K must be a multiple of 128")
+    kb, nb = k // SCALE_BLOCK, (n + SCALE_BLOCK - 1) // SCALE_BLOCK
+    _check(tuple(a_scale.shape) == (g, m, kb), f"a_scale must be [{g}, {m}, {kb}]")
+    _check(tuple(b_scale.shape) == (g, nb, kb), f"b_scale must be [{g}, {nb}, {kb}]")
+    _check(a.stride(2) == 1 and b.stride(2) == 1 and c.stride(2) == 1, "a, b need K contiguous, c needs N contiguous")
+    for name, t in (("a", a), ("b", b)):
+        _check(t.stride(1) % 16 == 0 and t.stride(0) % 16 == 0 and t.data_ptr() % 16 == 0,
+               f"{name}: row pitch, group pitch and base address must be multiples of 16")
+    dev = a.device
+    _check(all(t.device == dev for t in (b, a_scale, b_scale, c)), "tensors on different devices")
+    if m_valid is not None:
+        _check(m_valid.is_cuda and m_valid.device == dev and m_valid.dtype == torch.int32
+               and tuple(m_valid.shape) == (g,) and m_valid.is_contiguous(), "m_valid must be a contiguous int32 CUDA tensor [G]")
+    if plan is not None:
+        _check(plan.cta_pair <= 0 and plan.split_k <= 1, "grouped launches use whole tiles on single CTAs")
+    if dev.index != torch.cuda.current_device():
+        with torch.cuda.device(dev):
+            return fp8_mm_grouped(a, b, a_scale, b_scale, c, m_valid, plan, check)
+    st = _status_words(dev)
+    cplan = plan.to_c() if plan is not None else None
+    rc = lib.b200_fp8_mm_grouped(
+        a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), c.data_ptr(), g, m, n, k,
+        a.stride(1), a.stride(0), b.stride(1), b.stride(0),
+        a_scale.stride(0), a_scale.stride(1), a_scale.stride(2),
+        b_scale.stride(0), b_scale.stride(1), b_scale.stride(2),
+        c.stride(1), c.stride(0),
+        m_valid.data_ptr() if m_valid is not None else None,
+        st.data_ptr(), torch.cuda.current_stream(dev).cuda_stream,
+        ctypes.byref(cplan) if cplan is not None else None)
+    if rc != 0:
+        raise Fp8MmError(rc, f"G={g} M={m} N={n} K={k}")
+    if check:
+        check_device_status(dev)
+    return c
+
+
 def check_device_status(device=None):
     """Synchronises and raises Fp8MmDeviceError if any launch since the last check gave up a wait."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

@@ -274,6 +274,33 @@ def run_ours(args):
     ms = max_over_ranks(ms_local)
     check_device_status(dev)
 
+    # The same GEMM with a and b in the harness's MN-major storage ([K][M], [K][N]), consumed in place.
+    mn_ms = None
+    if world == 1:
+        from amd_developer_challenge_2025_b200.inputs import mn_major
+        a0, b0, as0, bs0, c0 = sets[0]
+        am, bm = mn_major(a0), mn_major(b0)
+        mn_fn = lambda: pkg.fp8_mm(am, bm, as0, bs0, c0)
+        mn_ms = time_launches([mn_fn], min(args.steps, 50), 3)
+        check_device_status(dev)
+        del am, bm
+
+    # Optional all-gather of the column shards of c (not part of the timed GEMM; reported beside it).
+    gather_ms = None
+    if dist is not None and n % world == 0:
+        gathered = torch.empty(world, m, n_loc, dtype=torch.bfloat16, device=dev)
+        for _ in range(3):
+            dist.all_gather_into_tensor(gathered, sets[0][4])
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(10):
+            dist.all_gather_into_tensor(gathered, sets[0][4])
+        g1.record()
+        torch.cuda.synchronize()
+        gather_ms = max_over_ranks(g0.elapsed_time(g1) / 10)
+        del gathered
+
     # end to end through the public call with host buffers (pinned), copies inside the timed region
     ha, hb, has_, hbs = (t.cpu().pin_memory() for t in sets[0][:4])
     hc = torch.empty(m, n_loc, dtype=torch.bfloat16).pin_memory()
@@ -362,6 +389,13 @@ def run_ours(args):
             "gpu_launches": args.steps,
             "clocks": clocks,
         }
+        if mn_ms is not None:
+            line["mn_major_operands"] = {"ms_per_step": round(mn_ms, 5),
+                                         "value": round(flops / (mn_ms * 1e-3) / 1e12, 2), "unit": UNIT}
+        if gather_ms is not None:
+            line["all_gather_c"] = {"ms": round(gather_ms, 4), "bytes_per_rank": 2 * m * n_loc,
+                                    "note": "NCCL all_gather_into_tensor of the bf16 shards into [ranks, M, N/ranks]; "
+                                            "outside the timed GEMM"}
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
         if per_shape:

@@ -146,6 +146,37 @@ int b200_fp8_mm_strided(const void* a, const void* b, const float* a_scale, cons
                         const b200_fp8_mm_plan* forced);
 
 /*
+ * Grouped form: `groups` independent block-scaled GEMMs of the same N and K in one launch, for the
+ * expert GEMMs of an MoE layer. (The reference's MoE submission runs its experts as fp16
+ * `torch.bmm` calls, 2-amd-moe/amd-moe-submission.py:604-611; this is the FP8 block-scaled kernel
+ * offered for that call site, one launch instead of one per expert.)
+ *
+ *  a        e4m3fn [groups][M][K],  element (g,i,kk) at a + g*a_g + i*lda + kk
+ *  b        e4m3fn [groups][N][K],  element (g,j,kk) at b + g*b_g + j*ldb + kk
+ *  a_scale  fp32, element (g,i,kb)  at a_scale + g*sa_g + i*sa_m + kb*sa_k
+ *  b_scale  fp32, element (g,jb,kb) at b_scale + g*sb_g + jb*sb_n + kb*sb_k, jb = j/128
+ *  c        bf16 [groups][M][N],    element (g,i,j) at c + g*c_g + i*ldc + j
+ *  m_valid  NULL, or a DEVICE array int[groups]: only rows [0, m_valid[g]) of group g exist
+ *           (clamped to [0, M]). Tiles past it are skipped, rows past it are not written. The
+ *           array is read by the kernel, so it may be produced on the stream just before.
+ *  lda, ldb, a_g, b_g multiples of 16; a and b 16-byte aligned; K a multiple of 128
+ *  forced   NULL, or a plan (block_n, stages, store_bufs are read); every tile is whole:
+ *           split_k > 1 or cta_pair = 1 give B200_FP8_MM_ERR_PLAN
+ *
+ * Needs no workspace. Asynchronous; inputs are never written.
+ */
+int b200_fp8_mm_grouped(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c,
+                        int groups, int M, int N, int K,
+                        long long lda, long long a_g,
+                        long long ldb, long long b_g,
+                        long long sa_g, long long sa_m, long long sa_k,
+                        long long sb_g, long long sb_n, long long sb_k,
+                        long long ldc, long long c_g,
+                        const int* m_valid,
+                        int* device_status, void* stream,
+                        const b200_fp8_mm_plan* forced);
+
+/*
  * The same GEMM for callers that cannot allocate device memory. (No counterpart in the
  * reference: its launcher gets its split-K scratch from torch.empty on every call.)
  *
