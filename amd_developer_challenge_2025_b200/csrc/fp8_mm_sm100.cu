@@ -491,6 +491,7 @@ struct WorkItem {
 
 // Work item w -> tile and K range. Tiles are walked in groups of raster_group tile rows, column
 // by column inside a group, so that the CTAs running at one time share A and B tiles in L2.
+template <bool GENERIC>
 __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, int tile_m, int block_n) {
   WorkItem it;
   int t;
@@ -509,7 +510,7 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
   it.tile = t;
   it.group = 0;
   it.m_limit = p.M;
-  if (p.groups > 0) {
+  if (GENERIC && p.groups > 0) {
     const int per_problem = p.tiles_m * p.tiles_n;
     it.group = t / per_problem;
     t -= it.group * per_problem;
@@ -524,7 +525,7 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
   const int tn = within / gsize;
   it.m0 = tm * tile_m;
   it.n0 = tn * block_n;
-  it.skip = it.m0 >= it.m_limit;
+  it.skip = GENERIC && it.m0 >= it.m_limit;
   it.kb_begin = static_cast<int>((static_cast<long long>(it.split) * p.kblocks) / it.nsplit);
   it.kb_end = static_cast<int>((static_cast<long long>(it.split + 1) * p.kblocks) / it.nsplit);
   return it;
@@ -534,7 +535,10 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
 // The kernel
 // ---------------------------------------------------------------------------------------------
 
-template <int BN, bool PAIR>
+// GENERIC = false is the plain case (K-major a and b, one problem): operand layout and work list are
+// compile-time facts and none of the MN-major / grouped code is in the instruction stream of the
+// single-thread roles, whose per-K-block instruction count is on the critical path of narrow tiles.
+template <int BN, bool PAIR, bool GENERIC>
 __global__ void __launch_bounds__((TileCfg<BN, PAIR>::kThreads), 1)
 fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const __grid_constant__ CUtensorMap tmap_c, const KernelParams p) {
@@ -600,7 +604,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  const int all_tiles = p.tiles_m * p.tiles_n * (p.groups > 0 ? p.groups : 1);
+  const int all_tiles = p.tiles_m * p.tiles_n * ((GENERIC && p.groups > 0) ? p.groups : 1);
   const int total_work = p.full_tiles + (all_tiles - p.full_tiles) * p.split_k;
   const int work_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int work_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
@@ -614,7 +618,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         uint32_t phase = 0;
         bool ok = true;
         for (int w = work_first; w < total_work && ok; w += work_step) {
-          const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+          const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
           if (it.skip) continue;
           const int a_row = it.m0 + static_cast<int>(cta_rank) * kBlockM;
           const int b_row = it.n0 + static_cast<int>(cta_rank) * (PAIR ? Cfg::kRowsB : 0);
@@ -628,16 +632,16 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             mbar_expect_tx_cluster(fb, Cfg::kStageBytes);
             const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
             // K-major: x = byte of K, y = matrix row. MN-major: x = matrix row (a multiple of 64), y = k.
-            if (p.groups > 0) {
+            if (GENERIC && p.groups > 0) {
               tma_load_3d(sa, &tmap_a, kb * kBlockK, a_row, it.group, fb);
               tma_load_3d(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
             } else {
-            if (!p.a_mn) {
+            if (!GENERIC || !p.a_mn) {
               tma_load_2d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, fb);
             } else {
               tma_load_2d<PAIR>(sa, &tmap_a, a_row, kb * kBlockK, fb);
             }
-            if (!p.b_mn) {
+            if (!GENERIC || !p.b_mn) {
               tma_load_2d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, fb);
             } else {
               for (int i = 0; i < p.b_boxes; ++i)
@@ -660,8 +664,11 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       // about 700 clocks per K block on its barrier wait and on issuing (an MMA costs the issuing
       // thread roughly 100 clocks), more than the tensor pipe needs for a narrow tile's block.
       if (lane == 0 && cta_rank == 0 && warp - 1 < p.issuers) {
-        const uint32_t idesc = make_idesc(Cfg::kTileM, BN) | p.idesc_major;
-        const uint32_t a_hi = p.a_desc_hi, b_hi = p.b_desc_hi, a_kstep = p.a_kstep, b_kstep = p.b_kstep;
+        constexpr uint32_t kHiK = (1024u >> 4) | (1u << 14) | (2u << 29);  // K-major, 128-byte swizzle
+        const uint32_t idesc = make_idesc(Cfg::kTileM, BN) | (GENERIC ? p.idesc_major : 0u);
+        const uint32_t a_hi = GENERIC ? p.a_desc_hi : kHiK, b_hi = GENERIC ? p.b_desc_hi : kHiK;
+        const uint32_t a_kstep = GENERIC ? p.a_kstep : 2u, b_kstep = GENERIC ? p.b_kstep : 2u;
+        const uint32_t a_lo_bits = GENERIC ? p.a_desc_lo : (1u << 16), b_lo_bits = GENERIC ? p.b_desc_lo : (1u << 16);
         const int me = warp - 1;
         // Both issuers walk every K block and keep the ring position with increments only (no
         // division on this thread: its scalar work is on the critical path); each issues for the
@@ -670,7 +677,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         uint32_t phase = 0;
         bool ok = true;
         for (int w = work_first; w < total_work && ok; w += work_step) {
-          const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+          const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
           if (it.skip) continue;
           for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
             const bool mine = (turn == me);
@@ -684,8 +691,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             if (++buf == nbufs) buf = 0;
             if (!mine) continue;
             const uint32_t sa = smem_u32(smem + my_stage * Cfg::kStageBytes);
-            const uint32_t a_lo = smem_desc_addr(sa) | p.a_desc_lo;
-            const uint32_t b_lo = smem_desc_addr(sa + Cfg::kStageBytesA) | p.b_desc_lo;
+            const uint32_t a_lo = smem_desc_addr(sa) | a_lo_bits;
+            const uint32_t b_lo = smem_desc_addr(sa + Cfg::kStageBytesA) | b_lo_bits;
             const uint32_t d_addr = tmem_base + static_cast<uint32_t>(my_buf * BN);
             // operands landed AND the TMEM buffer of this K block drained (see the promotion warps)
             if (!mbar_wait(smem_u32(&full_bar[my_stage]), my_phase, ctx, 0x300 | my_stage)) {
@@ -711,7 +718,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       uint32_t sphase = 0;
       bool ok = true;
       for (int w = work_first; w < total_work && ok; w += work_step) {
-        const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+        const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
         if (it.skip) continue;
         const int row0 = it.m0 + static_cast<int>(cta_rank) * kBlockM;
         const float* a_base = p.a_scale + static_cast<long long>(it.group) * p.sa_g;
@@ -784,7 +791,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     bool ok = true;
 
     for (int w = work_first; w < total_work && ok; w += work_step) {
-      const WorkItem it = decode_work(p, w, Cfg::kTileM, BN);
+      const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
       if (it.skip) continue;
       const int row = it.m0 + static_cast<int>(cta_rank) * kBlockM + row_in_tile;
       // Index of this thread's first b_scale row inside a ring slot (at most 2 rows per 128 columns).
@@ -915,7 +922,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       }
       // The TMA store clips at the tensor's edges only: a tile that a group's row count cuts short goes out
       // through the guarded plain stores instead.
-      const bool tma_rows_ok = (it.m_limit == p.M) || (it.m0 + Cfg::kTileM <= it.m_limit);
+      const bool tma_rows_ok = !GENERIC || (it.m_limit == p.M) || (it.m0 + Cfg::kTileM <= it.m_limit);
       if (do_store && p.store_bufs > 0 && tma_rows_ok) {
         // bf16 tile -> swizzled staging -> TMA store, 32 columns at a time per warpgroup. The
         // 16-byte piece q of row r sits at r*64 + ((q ^ ((r >> 1) & 3)) * 16) (SWIZZLE_64B), which
@@ -949,7 +956,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           wg_bar_sync(half);
           if (wg_tid == 0) {
-            if (p.groups > 0) {
+            if (GENERIC && p.groups > 0) {
               tma_store_3d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols, it.m0,
                            it.group);
             } else {
@@ -1270,12 +1277,23 @@ bool plan_is_supported(const b200_fp8_mm_plan& pl, int kblocks) {
 
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const KernelParams);
 
-KernelFn kernel_for(int block_n, int pair) {
+// generic: MN-major operands or a grouped launch (single CTAs only).
+KernelFn kernel_for(int block_n, int pair, bool generic) {
+  if (generic) {
+    if (pair) return nullptr;
+    switch (block_n) {
+      case 64: return fp8_mm_blockscaled_kernel<64, false, true>;
+      case 128: return fp8_mm_blockscaled_kernel<128, false, true>;
+      case 192: return fp8_mm_blockscaled_kernel<192, false, true>;
+      case 256: return fp8_mm_blockscaled_kernel<256, false, true>;
+      default: return nullptr;
+    }
+  }
   switch (block_n) {
-    case 64: return pair ? fp8_mm_blockscaled_kernel<64, true> : fp8_mm_blockscaled_kernel<64, false>;
-    case 128: return pair ? fp8_mm_blockscaled_kernel<128, true> : fp8_mm_blockscaled_kernel<128, false>;
-    case 192: return pair ? fp8_mm_blockscaled_kernel<192, true> : fp8_mm_blockscaled_kernel<192, false>;
-    case 256: return pair ? fp8_mm_blockscaled_kernel<256, true> : fp8_mm_blockscaled_kernel<256, false>;
+    case 64: return pair ? fp8_mm_blockscaled_kernel<64, true, false> : fp8_mm_blockscaled_kernel<64, false, false>;
+    case 128: return pair ? fp8_mm_blockscaled_kernel<128, true, false> : fp8_mm_blockscaled_kernel<128, false, false>;
+    case 192: return pair ? fp8_mm_blockscaled_kernel<192, true, false> : fp8_mm_blockscaled_kernel<192, false, false>;
+    case 256: return pair ? fp8_mm_blockscaled_kernel<256, true, false> : fp8_mm_blockscaled_kernel<256, false, false>;
     default: return nullptr;
   }
 }
@@ -1354,7 +1372,7 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
                    (reinterpret_cast<uintptr_t>(workspace) % 256) != 0))
     return B200_FP8_MM_ERR_WORKSPACE;
 
-  KernelFn fn = kernel_for(pl.block_n, pl.cta_pair);
+  KernelFn fn = kernel_for(pl.block_n, pl.cta_pair, a_mn || b_mn);
   if (fn == nullptr) return B200_FP8_MM_ERR_PLAN;
 
   CUtensorMap map_a, map_b, map_c;
@@ -1431,10 +1449,11 @@ int launch(KernelFn fn, const b200_fp8_mm_plan& pl, const CUtensorMap& map_a, co
   // Opt every kernel in to the full 227 KiB of dynamic shared memory once per device.
   cudaError_t err = cudaSuccess;
   {
-    static unsigned char opted_in[64][8] = {};
+    static unsigned char opted_in[64][12] = {};
     int dev = 0;
     (void)cudaGetDevice(&dev);
-    const int slot = (pl.block_n / 64 - 1) * 2 + (pl.cta_pair ? 1 : 0);
+    const bool generic = kp.groups > 0 || kp.a_mn || kp.b_mn;
+    const int slot = generic ? 8 + (pl.block_n / 64 - 1) : (pl.block_n / 64 - 1) * 2 + (pl.cta_pair ? 1 : 0);
     if (dev < 0 || dev >= 64 || !opted_in[dev][slot]) {
       err = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kMaxSmem);
@@ -1500,7 +1519,7 @@ int run_grouped(const void* a, const void* b, const float* a_scale, const float*
   b200_fp8_mm_plan pl;
   choose_plan(groups * tiles_m * kBlockM, N, K, sm_count, &forced, &pl);
   if (!plan_is_supported(pl, K / kBlockK) || pl.split_k != 1 || pl.cta_pair != 0) return B200_FP8_MM_ERR_PLAN;
-  KernelFn fn = kernel_for(pl.block_n, 0);
+  KernelFn fn = kernel_for(pl.block_n, 0, true);
   if (fn == nullptr) return B200_FP8_MM_ERR_PLAN;
 
   CUtensorMap map_a, map_b, map_c;

@@ -70,10 +70,10 @@ def dequant_reference(a, b, a_scale, b_scale):
     return (a32 @ b32.T).to(torch.bfloat16)
 
 
-def run_test(cases, device="cuda"):
+def run_test(cases, device="cuda", layout="k"):
     results = []
     for (m, n, k, seed) in cases:
-        data = make_inputs(m, n, k, seed, device=device)
+        data = make_inputs(m, n, k, seed, device=device, layout=layout)
         out = custom_kernel(data)
         check_device_status(device)
         ref = dequant_reference(*data[:4]).float()
@@ -84,10 +84,10 @@ def run_test(cases, device="cuda"):
     return results
 
 
-def run_benchmark(cases, device="cuda", reps=50, warmup=5):
+def run_benchmark(cases, device="cuda", reps=50, warmup=5, layout="k"):
     results = []
     for (m, n, k, seed) in cases:
-        data = make_inputs(m, n, k, seed, device=device)
+        data = make_inputs(m, n, k, seed, device=device, layout=layout)
         for _ in range(warmup):
             custom_kernel(data)
         check_device_status(device)
@@ -116,6 +116,8 @@ def main(argv=None):
     ap.add_argument("spec", nargs="?", help="spec file; omit with --competition-shapes")
     ap.add_argument("--competition-shapes", action="store_true", help="the 2 x 9 shape grid the reference describes")
     ap.add_argument("--device", default="cuda")
+    ap.add_argument("--layout", choices=("k", "mn"), default="k",
+                    help="storage of a and b: K contiguous, or the harness's [K][M] / [K][N] (mn)")
     args = ap.parse_args(argv)
     if args.competition_shapes:
         cases = competition_cases()
@@ -127,9 +129,9 @@ def main(argv=None):
     if not torch.cuda.is_available():
         sys.exit("the operator needs a CUDA device: there is no CPU path")
     if args.mode == "test":
-        results = run_test(cases, args.device)
+        results = run_test(cases, args.device, layout=args.layout)
         sys.exit(0 if all(r["pass"] for r in results) else 1)
-    run_benchmark(cases, args.device)
+    run_benchmark(cases, args.device, layout=args.layout)
 
 
 if __name__ == "__main__":

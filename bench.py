@@ -285,6 +285,29 @@ def run_ours(args):
         check_device_status(dev)
         del am, bm
 
+    # Grouped launch (expert GEMMs of an MoE layer): 8 groups of 1024 x 2048 x 7168 in one kernel, beside the same
+    # eight problems as separate launches.
+    grouped = None
+    if world == 1 and not args.shape and not args.no_sweep:
+        gg, gm, gn, gk = 8, 1024, 2048, 7168
+        parts = [gpu_inputs(gm, gn, gk, 4000 + i, dev) for i in range(gg)]
+        ga, gb, gas, gbs = (torch.stack([p_[j] for p_ in parts]) for j in range(4))
+        gc = torch.empty(gg, gm, gn, dtype=torch.bfloat16, device=dev)
+        del parts
+        one = lambda: pkg.fp8_mm_grouped(ga, gb, gas, gbs, gc)
+        sep = lambda: [pkg.fp8_mm(ga[i], gb[i], gas[i], gbs[i], gc[i]) for i in range(gg)]
+        t_one = time_launches([one], 30, 3)
+        t_sep = time_launches([sep], 30, 3)
+        gc.fill_(float("nan"))
+        one()  # what the check below looks at is the grouped launch's output
+        check_device_status(dev)
+        gflop = 2.0 * gg * gm * gn * gk
+        grouped = {"groups": gg, "m": gm, "n": gn, "k": gk, "ms": round(t_one, 5),
+                   "tflops": round(gflop / (t_one * 1e-3) / 1e12, 1),
+                   "separate_launches_ms": round(t_sep, 5),
+                   "pass": bool(spot_check(pkg, ga[3], gb[3], gas[3], gbs[3], gc[3], rows=64))}
+        del ga, gb, gas, gbs, gc
+
     # Optional all-gather of the column shards of c (not part of the timed GEMM; reported beside it).
     gather_ms = None
     if dist is not None and n % world == 0:
@@ -392,6 +415,8 @@ def run_ours(args):
         if mn_ms is not None:
             line["mn_major_operands"] = {"ms_per_step": round(mn_ms, 5),
                                          "value": round(flops / (mn_ms * 1e-3) / 1e12, 2), "unit": UNIT}
+        if grouped is not None:
+            line["grouped"] = grouped
         if gather_ms is not None:
             line["all_gather_c"] = {"ms": round(gather_ms, 4), "bytes_per_rank": 2 * m * n_loc,
                                     "note": "NCCL all_gather_into_tensor of the bf16 shards into [ranks, M, N/ranks]; "
