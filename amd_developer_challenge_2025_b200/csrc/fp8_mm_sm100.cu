@@ -670,26 +670,19 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const uint32_t a_kstep = GENERIC ? p.a_kstep : 2u, b_kstep = GENERIC ? p.b_kstep : 2u;
         const uint32_t a_lo_bits = GENERIC ? p.a_desc_lo : (1u << 16), b_lo_bits = GENERIC ? p.b_desc_lo : (1u << 16);
         const int me = warp - 1;
-        // Both issuers walk every K block and keep the ring position with increments only (no
-        // division on this thread: its scalar work is on the critical path); each issues for the
-        // K blocks whose turn it is.
-        int stage = 0, buf = 0, turn = 0;
-        uint32_t phase = 0;
+        // Each issuer visits only its own K blocks (every issuers-th one of the CTA's whole sequence, across
+        // tile boundaries) and keeps its ring position with add-and-wrap only: no division and no work for
+        // the other issuer's blocks on this thread, whose scalar instructions are on the critical path.
+        const int step = p.issuers;
+        int my_stage = me % stages, my_buf = me % nbufs;
+        uint32_t my_phase = (me / stages) & 1u;
+        int first = me;  // offset of this issuer's next K block from the start of the next tile
         bool ok = true;
         for (int w = work_first; w < total_work && ok; w += work_step) {
           const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
           if (it.skip) continue;
-          for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
-            const bool mine = (turn == me);
-            if (++turn == p.issuers) turn = 0;
-            const int my_stage = stage, my_buf = buf;
-            const uint32_t my_phase = phase;
-            if (++stage == stages) {
-              stage = 0;
-              phase ^= 1u;
-            }
-            if (++buf == nbufs) buf = 0;
-            if (!mine) continue;
+          int kb = it.kb_begin + first;
+          for (; kb < it.kb_end; kb += step) {
             const uint32_t sa = smem_u32(smem + my_stage * Cfg::kStageBytes);
             const uint32_t a_lo = smem_desc_addr(sa) | a_lo_bits;
             const uint32_t b_lo = smem_desc_addr(sa + Cfg::kStageBytesA) | b_lo_bits;
@@ -706,7 +699,15 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               umma_f8<PAIR>(d_addr, a_lo + a_kstep * k, b_lo + b_kstep * k, a_hi, b_hi, idesc, k > 0 ? 1u : 0u);
             }
             umma_commit<PAIR>(smem_u32(&done_bar[my_stage]));
+            my_stage += step;
+            if (my_stage >= stages) {
+              my_stage -= stages;
+              my_phase ^= 1u;
+            }
+            my_buf += step;
+            while (my_buf >= nbufs) my_buf -= nbufs;
           }
+          first = kb - it.kb_end;
         }
       }
       __syncwarp();
