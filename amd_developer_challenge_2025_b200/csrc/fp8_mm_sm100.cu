@@ -66,6 +66,8 @@ constexpr int kStoreBufBytes = kBlockM * kStoreBoxCols * 2;      // one staging 
 constexpr int kScaleGroup = 4;                                   // K blocks per scale-ring slot
 constexpr int kScaleSlots = 4;                                   // ring depth (16 K blocks)
 constexpr int kScaleSlotFloats = kBlockM * kScaleGroup + 4 * kScaleGroup;  // a[128][4] + b[4][4]
+constexpr int kBarrierBytes = 512;                                         // mbarriers and flags
+constexpr int kHeaderBytes = ((kBarrierBytes + kScaleSlots * kScaleSlotFloats * 4 + 1023) / 1024) * 1024;
 
 struct KernelParams {
   const float* a_scale;
@@ -548,8 +550,11 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int stages = p.stages;
   const int nbufs = p.tmem_bufs;
-  float* scale_ring = reinterpret_cast<float*>(smem + stages * Cfg::kStageBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(scale_ring + kScaleSlots * kScaleSlotFloats);
+  // Barriers, flags and the scale ring sit at fixed offsets in front of the operand ring, so that every
+  // role can form their addresses from one base register.
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  float* scale_ring = reinterpret_cast<float*>(smem + kBarrierBytes);
+  uint8_t* ring = smem + kHeaderBytes;
   uint64_t* full_bar = bars;                                 // [kMaxStages]
   uint64_t* done_bar = bars + kMaxStages;                    // [kMaxStages]
   uint64_t* scale_full_bar = bars + 2 * kMaxStages + 8;      // [kScaleSlots]
@@ -557,9 +562,9 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(scale_empty_bar + kScaleSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
-  // staging for the TMA store of c: [warpgroup][buffer][128 rows x 64 B], 1024-byte aligned
-  uint8_t* staging = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(bars) + 512 + 1023) & ~uintptr_t(1023));
+  // staging for the TMA store of c: [warpgroup][buffer][128 rows x 64 B], behind the ring (1024-byte aligned:
+  // the header and every stage are multiples of 1024 bytes)
+  uint8_t* staging = ring + stages * Cfg::kStageBytes;
 
   const int warp = static_cast<int>(threadIdx.x) >> 5;
   const int lane = static_cast<int>(threadIdx.x) & 31;
@@ -602,22 +607,28 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   __syncthreads();
   if constexpr (PAIR) cluster_sync_all();  // the peer's barriers are initialised before any remote arrive
   tcgen05_fence_after();
-  const uint32_t tmem_base = *tmem_base_slot;
+  // The TMEM base address is read again inside each role instead of being carried across the register
+  // re-allocation below: a value that is live in every role at once gets one register for all of them, which
+  // the promotion warps' accumulators then push out to local memory for everybody.
 
-  const int all_tiles = p.tiles_m * p.tiles_n * ((GENERIC && p.groups > 0) ? p.groups : 1);
-  const int total_work = p.full_tiles + (all_tiles - p.full_tiles) * p.split_k;
-  const int work_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  const int work_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  // The extent of the work list (kept out of registers across the role split for the same reason).
+  auto work_total = [&]() {
+    const int all_tiles = p.tiles_m * p.tiles_n * ((GENERIC && p.groups > 0) ? p.groups : 1);
+    return p.full_tiles + (all_tiles - p.full_tiles) * p.split_k;
+  };
+  auto work_begin = [&]() { return PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x); };
+  auto work_stride = [&]() { return PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x); };
 
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::kRegsLight));
     if (warp == 0) {
       // ---------------- TMA producer ----------------
       if (lane == 0) {
+        const int total_work = work_total(), work_step = work_stride();
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int w = work_first; w < total_work && ok; w += work_step) {
+        for (int w = work_begin(); w < total_work && ok; w += work_step) {
           const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
           if (it.skip) continue;
           const int a_row = it.m0 + static_cast<int>(cta_rank) * kBlockM;
@@ -630,7 +641,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             // Both CTAs of a pair report to the leader's barrier: its MMA thread consumes the stage.
             const uint32_t fb = PAIR ? map_to_cta(smem_u32(&full_bar[stage]), 0) : smem_u32(&full_bar[stage]);
             mbar_expect_tx_cluster(fb, Cfg::kStageBytes);
-            const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+            const uint32_t sa = smem_u32(ring + stage * Cfg::kStageBytes);
             // K-major: x = byte of K, y = matrix row. MN-major: x = matrix row (a multiple of 64), y = k.
             if (GENERIC && p.groups > 0) {
               tma_load_3d(sa, &tmap_a, kb * kBlockK, a_row, it.group, fb);
@@ -670,6 +681,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const uint32_t a_kstep = GENERIC ? p.a_kstep : 2u, b_kstep = GENERIC ? p.b_kstep : 2u;
         const uint32_t a_lo_bits = GENERIC ? p.a_desc_lo : (1u << 16), b_lo_bits = GENERIC ? p.b_desc_lo : (1u << 16);
         const int me = warp - 1;
+        const int total_work = work_total(), work_step = work_stride();
+        const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
         // Each issuer visits only its own K blocks (every issuers-th one of the CTA's whole sequence, across
         // tile boundaries) and keeps its ring position with add-and-wrap only: no division and no work for
         // the other issuer's blocks on this thread, whose scalar instructions are on the critical path.
@@ -678,12 +691,12 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         uint32_t my_phase = (me / stages) & 1u;
         int first = me;  // offset of this issuer's next K block from the start of the next tile
         bool ok = true;
-        for (int w = work_first; w < total_work && ok; w += work_step) {
+        for (int w = work_begin(); w < total_work && ok; w += work_step) {
           const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
           if (it.skip) continue;
           int kb = it.kb_begin + first;
           for (; kb < it.kb_end; kb += step) {
-            const uint32_t sa = smem_u32(smem + my_stage * Cfg::kStageBytes);
+            const uint32_t sa = smem_u32(ring + my_stage * Cfg::kStageBytes);
             const uint32_t a_lo = smem_desc_addr(sa) | a_lo_bits;
             const uint32_t b_lo = smem_desc_addr(sa + Cfg::kStageBytesA) | b_lo_bits;
             const uint32_t d_addr = tmem_base + static_cast<uint32_t>(my_buf * BN);
@@ -715,10 +728,11 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       // ---------------- scale loader ----------------
       // One ring slot holds the scales of kScaleGroup consecutive K blocks of the current tile:
       // a[row][u] for the CTA's 128 rows and b[j][u] for the (up to 4) b_scale rows the tile touches.
+      const int total_work = work_total(), work_step = work_stride();
       int slot = 0;
       uint32_t sphase = 0;
       bool ok = true;
-      for (int w = work_first; w < total_work && ok; w += work_step) {
+      for (int w = work_begin(); w < total_work && ok; w += work_step) {
         const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
         if (it.skip) continue;
         const int row0 = it.m0 + static_cast<int>(cta_rank) * kBlockM;
@@ -764,6 +778,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     // ---------------- promotion + store ----------------
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::kRegsHeavy));
     const int ew = warp - 4;
+    const int total_work = work_total(), work_step = work_stride();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) belong to warps with this id mod 4
     const int half = ew >> 2;      // column group of this warp: which share of the tile's columns
     const int row_in_tile = quarter * 32 + lane;
@@ -791,7 +807,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     uint32_t cphase = 0, sphase = 0;
     bool ok = true;
 
-    for (int w = work_first; w < total_work && ok; w += work_step) {
+    for (int w = work_begin(); w < total_work && ok; w += work_step) {
       const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
       if (it.skip) continue;
       const int row = it.m0 + static_cast<int>(cta_rank) * kBlockM + row_in_tile;
@@ -1004,6 +1020,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   if constexpr (PAIR) cluster_sync_all();
   if (warp == 2) {
     tcgen05_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
     if constexpr (PAIR) {
       asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols)
                    : "memory");
@@ -1111,11 +1128,9 @@ int epi_warps_for(int block_n) {
 
 int smem_bytes_for(int block_n, int stages, int pair, int store_bufs) {
   const int stage = kBlockM * kBlockK + (pair ? block_n / 2 : block_n) * kBlockK;
-  int bytes = stages * stage + kScaleSlots * kScaleSlotFloats * 4 + 512 /* barriers and flags */ +
-              1024 /* alignment slack */;
-  // staging of c for the TMA store: one area of store_bufs buffers per group of four promotion
-  // warps, 1024-byte aligned
-  if (store_bufs > 0) bytes += 1024 + (epi_warps_for(block_n) / 4) * store_bufs * kStoreBufBytes;
+  int bytes = 1024 /* alignment slack */ + kHeaderBytes /* barriers, flags, scale ring */ + stages * stage;
+  // staging of c for the TMA store: one area of store_bufs buffers per group of four promotion warps
+  if (store_bufs > 0) bytes += (epi_warps_for(block_n) / 4) * store_bufs * kStoreBufBytes;
   return bytes;
 }
 

@@ -50,6 +50,44 @@ def test_error_codes_without_launch(built_library):
     assert "unknown" in _lib.strerror(99)
 
 
+def test_error_codes_of_the_strided_and_grouped_entry_points(built_library):
+    from amd_developer_challenge_2025_b200 import _lib
+
+    lib = _lib.load()
+    one = ctypes.c_void_p(4096)  # never dereferenced: every check below fails first
+
+    def strided(a=one, m=128, n=128, k=128, a_sm=None, a_sk=1, b_sn=None, b_sk=1, plan=None):
+        return lib.b200_fp8_mm_strided(a, one, one, one, one, m, n, k, k if a_sm is None else a_sm, a_sk,
+                                       k if b_sn is None else b_sn, b_sk, 1, 1, 1, 1, n, 0, None, 0, None, None, plan)
+
+    assert strided(a=None) == 1 and strided(k=64) == 2
+    assert strided(a_sm=2, a_sk=2) == 3             # neither K nor M contiguous
+    assert strided(a_sm=1, a_sk=120) == 3           # MN-major with a pitch smaller than M
+    assert strided(a_sm=1, a_sk=136) == 3           # MN-major pitch not a multiple of 16
+    assert strided(b_sn=1, b_sk=100) == 3
+
+    def grouped(a=one, g=2, m=128, n=128, k=128, lda=None, a_g=None, ldb=None, b_g=None, ldc=None, c_g=None,
+                plan=None):
+        lda, ldb, ldc = lda or k, ldb or k, ldc or n
+        return lib.b200_fp8_mm_grouped(a, one, one, one, one, g, m, n, k, lda, a_g or m * lda, ldb, b_g or n * ldb,
+                                       m, 1, 1, 1, 1, 1, ldc, c_g or m * ldc, None, None, None, plan)
+
+    assert grouped(a=None) == 1
+    assert grouped(g=0) == 2 and grouped(k=100) == 2 and grouped(m=0) == 2
+    assert grouped(lda=100) == 3 and grouped(a_g=1000) == 3 and grouped(c_g=64) == 3
+    assert grouped(a=ctypes.c_void_p(4104)) == 4
+    assert len(_lib.strerror(10)) > 0
+
+
+def test_grouped_wrapper_rejects_cpu_tensors(built_library):
+    import amd_developer_challenge_2025_b200 as pkg
+
+    parts = [pkg.make_inputs(8, 128, 128, seed=i) for i in range(2)]
+    a, b, a_s, b_s, c = (torch.stack([p[j] for p in parts]) for j in range(5))
+    with pytest.raises(ValueError, match="CUDA"):
+        pkg.fp8_mm_grouped(a, b, a_s, b_s, c)
+
+
 def test_python_wrapper_rejects_cpu_tensors_and_bad_shapes(built_library):
     import amd_developer_challenge_2025_b200 as pkg
 
