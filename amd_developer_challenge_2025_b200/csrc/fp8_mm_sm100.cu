@@ -1182,7 +1182,11 @@ struct WidthCost {
   double per_kblock, per_tile, split_const, per_split;
 };
 
-WidthCost width_cost(int bn) {
+WidthCost width_cost(int bn, int pair) {
+  // CTA pairs: each CTA loads half of the B tile, which pays per K block at the 192-wide tile (5 % fewer
+  // clocks; long-K shapes gain 3-6 %, K <= 512 loses 2-5 % to the dearer tile turnaround). At the other
+  // widths pairs measured slower throughout.
+  if (pair && bn == 192) return {775.0, 3600.0, 8500.0, 1000.0};
   switch (bn) {
     case 64: return {400.0, 1850.0, 6500.0, 750.0};
     case 128: return {585.0, 2500.0, 9000.0, 1100.0};
@@ -1190,6 +1194,9 @@ WidthCost width_cost(int bn) {
     default: return {1330.0, 4400.0, 11000.0, 1500.0};
   }
 }
+
+// What a pair plan's cost is multiplied by, for the widths without a table of their own.
+double pair_penalty(int bn) { return bn == 192 ? 1.0 : (bn == 256 ? 1.35 : 1.04); }
 
 struct Candidate {
   int bn, pair, split, full_tiles;
@@ -1202,7 +1209,7 @@ struct Candidate {
 Candidate evaluate(int M, int N, int kblocks, int sm_count, int bn, int pair, int forced_split) {
   const int tiles = ceil_div(M, pair ? 2 * kBlockM : kBlockM) * ceil_div(N, bn);
   const int units = pair ? sm_count / 2 : sm_count;
-  const WidthCost wc = width_cost(bn);
+  const WidthCost wc = width_cost(bn, pair);
   const int per_unit = pair ? 2 : 1;
   auto cap_split = [&](int s) {
     if (s > kblocks / 4) s = kblocks / 4;
@@ -1211,7 +1218,7 @@ Candidate evaluate(int M, int N, int kblocks, int sm_count, int bn, int pair, in
   };
   Candidate best{bn, pair, 1, tiles, ceil_div(tiles, units) * (kblocks * wc.per_kblock + wc.per_tile)};
   if (forced_split == 1 || kblocks < 8) {
-    if (pair) best.cost *= 1.04;
+    if (pair) best.cost *= pair_penalty(bn);
     return best;
   }
   if (tiles * 2 <= units || (forced_split > 1 && tiles <= units)) {
@@ -1233,7 +1240,7 @@ Candidate evaluate(int M, int N, int kblocks, int sm_count, int bn, int pair, in
       if (cost < best.cost || forced_split > 1) best = Candidate{bn, pair, split, tiles - tail, cost};
     }
   }
-  if (pair) best.cost *= 1.04;  // measured: a few percent slower than single CTAs in short runs
+  if (pair) best.cost *= pair_penalty(bn);
   return best;
 }
 

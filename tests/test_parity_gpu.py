@@ -129,18 +129,33 @@ def test_every_kernel_variant(plan):
     assert_close(c, ref, str(plan) + " stages=2")
 
 
-@pytest.mark.parametrize("bn,split", [(192, 2), (128, 3), (64, 2)])
-def test_split_k_tail_of_a_partly_filled_last_wave(bn, split):
+@pytest.mark.parametrize("m,n,k", [(8192, 576, 7168), (8192, 2304, 1024), (4096, 4608, 512)])
+def test_automatic_plans_with_pairs_and_tails(m, n, k):
+    """Shapes whose automatic plan is a CTA pair with a split-K tail (or close to one): rows sampled against
+    the oracle, and the run repeated bit for bit."""
+    a, b, a_s, b_s, c = cuda_inputs(m, n, k, m + n)
+    c.fill_(float("nan"))
+    run(a, b, a_s, b_s, c)
+    rows = torch.tensor(sorted({0, 127, 128, 255, 256, m - 129, m - 1} | set(range(1000, 1040))), device="cuda")
+    assert_close(c[rows], oracle.dequant_matmul(a[rows], b, a_s[rows], b_s), f"{m}x{n}x{k} {pkg.describe(m, n, k)}")
+    assert torch.isfinite(c.float()).all()
+    c2 = torch.full_like(c, float("nan"))
+    run(a, b, a_s, b_s, c2)
+    assert torch.equal(c2.view(torch.int16), c.view(torch.int16))
+
+
+@pytest.mark.parametrize("bn,split,pair", [(192, 2, -1), (128, 3, -1), (64, 2, -1), (192, 3, 1), (128, 2, 1)])
+def test_split_k_tail_of_a_partly_filled_last_wave(bn, split, pair):
     """More tiles than SMs, not a whole number of waves: the full waves run whole tiles, the tail is
     split along K (whole and split tiles in one launch)."""
     m, n, k = 4096, 2304, 1024
     plan_probe = pkg.describe(m, n, k)
     a, b, a_s, b_s, c = cuda_inputs(m, n, k, 17)
     c.fill_(float("nan"))
-    plan = Plan(block_n=bn, cta_pair=-1, split_k=split)
+    plan = Plan(block_n=bn, cta_pair=pair, split_k=split)
     run(a, b, a_s, b_s, c, plan=plan)
     assert plan_probe.tiles > 0
-    assert_close(c, oracle.dequant_matmul(a, b, a_s, b_s), f"tail bn={bn} split={split}")
+    assert_close(c, oracle.dequant_matmul(a, b, a_s, b_s), f"tail bn={bn} split={split} pair={pair}")
     c2 = torch.full_like(c, float("nan"))
     run(a, b, a_s, b_s, c2, plan=plan)
     assert torch.equal(c2.view(torch.int16), c.view(torch.int16))
