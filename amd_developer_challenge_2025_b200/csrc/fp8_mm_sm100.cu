@@ -16,8 +16,8 @@
 //               which both frees the stage for the producer and publishes the buffer to the
 //               promotion warps. It waits on ONE barrier per K block: a stage's "full" barrier also
 //               collects the promotion warps' release of the TMEM buffer that K block will
-//               overwrite (stage s always pairs with buffer s mod buffers: the ring depth is a
-//               multiple of the buffer count)
+//               overwrite (K block j uses stage j mod stages and buffer j mod buffers; a warp that
+//               has drained the buffer of K block j arrives on the barrier of K block j + buffers)
 //   warp 2      allocates / frees TMEM; its first lane is a second MMA issuer (the two issuers take
 //               alternate K blocks)
 //   warp 3      scale loader: cp.async of the a_scale / b_scale values of FOUR K blocks at a time
@@ -1138,28 +1138,28 @@ constexpr int kMaxSmem = 232448;  // 227 KiB opt-in limit per CTA on sm_100
 
 int tmem_bufs_for(int block_n) { return block_n <= 128 ? 4 : 2; }
 
-// The kernel pairs stage s with TMEM buffer s mod buffers, so the buffers in use must divide the
-// ring depth: the largest such count the tile width allows.
+// K block j uses ring stage j mod stages and TMEM buffer j mod buffers; the two counts are independent
+// (the promotion warps release a buffer to the barrier of the stage that the K block `buffers` later will
+// use), except that a buffer cannot be re-used before its stage is: buffers <= stages.
 int tmem_bufs_in_use(int block_n, int stages) {
-  int d = tmem_bufs_for(block_n);
-  while (d > 1 && (stages % d) != 0) --d;
-  return d;
+  const int d = tmem_bufs_for(block_n);
+  return d < stages ? d : stages;
 }
 
-// Deepest ring that fits and is a multiple of the tile's TMEM buffer count.
+// Deepest ring that fits.
 int max_stages_for(int block_n, int pair, int store_bufs) {
-  const int bufs = tmem_bufs_for(block_n);
   int s = kMaxStages;
-  while (s > bufs && (smem_bytes_for(block_n, s, pair, store_bufs) > kMaxSmem || (s % bufs) != 0)) --s;
+  while (s > 2 && smem_bytes_for(block_n, s, pair, store_bufs) > kMaxSmem) --s;
   return s;
 }
 
-// Staging buffers for the TMA store of c. Tiles with few K blocks spend most of their time storing,
-// so they get two buffers (store of one box overlaps the staging of the next) even if that costs
-// pipeline stages; long-K tiles keep the deeper ring and one buffer.
+// Staging buffers for the TMA store of c: two (the store of one box overlaps the staging of the next)
+// unless that would leave fewer than four ring stages.
 int store_bufs_for(int block_n, int pair, int kblocks_per_item) {
   if (kblocks_per_item <= 8) return 2;
-  return max_stages_for(block_n, pair, 2) == max_stages_for(block_n, pair, 1) ? 2 : 1;
+  // measured: a second staging buffer is worth more than a fifth (single CTA) or seventh (pair) ring stage
+  const int with_two = max_stages_for(block_n, pair, 2);
+  return (with_two >= 4 || with_two == max_stages_for(block_n, pair, 1)) ? 2 : 1;
 }
 
 bool valid_block_n(int bn) { return bn == 64 || bn == 128 || bn == 192 || bn == 256; }
