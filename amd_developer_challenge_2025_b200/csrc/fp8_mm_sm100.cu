@@ -473,14 +473,18 @@ struct TileCfg {
   // Register split after setmaxnreg (light: producer / MMA / loader warps, heavy: promotion warps):
   // 128 * light + kEpiThreads * heavy is at most the allocation the CTA is launched with
   // (384 x 168 or 512 x 128 registers).
-  static constexpr int kRegsLight = (kEpiWarps == 12) ? 56 : (BN == 256 ? 72 : 104);
-  static constexpr int kRegsHeavy = (kEpiWarps == 12) ? 152 : (BN == 256 ? 216 : 200);
+  static constexpr int kRegsLight = 104;
+  static constexpr int kRegsHeavy = 200;
   // Columns fetched from TMEM per tcgen05.ld: as wide as the registers allow without spilling
   // next to the accumulators (a spill in this loop costs hundreds of clocks: local memory shares
   // the saturated shared-memory path). tcgen05.wait::ld waits for every outstanding fetch, so
   // several narrow fetches in flight would gain nothing.
   static constexpr int kChunkCols = (kColsPerThread == 64) ? 64 : 32;
   static constexpr int kChunks = kColsPerThread / kChunkCols;
+  // Accumulators as packed pairs (fma.rn.f32x2: half the issue slots) or as scalars. With 128 columns per
+  // thread the packed form spills (the pairs want aligned 64-bit registers next to a 32-register landing
+  // area); scalars fit, and the 256-wide pair plan went from 442 to 262 us on the headline GEMM.
+  static constexpr bool kScalarAcc = (BN == 256);
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "block_n must be 64, 128, 192 or 256");
 };
 
@@ -816,9 +820,12 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       const int jb0 = gcol0 >> 7;
       const int bi0 = jb0 - ((it.n0 + p.n_phase) >> 7);
 
-      unsigned long long acc2[Cfg::kColsPerThread / 2];  // column pairs (2j, 2j+1)
+      unsigned long long acc2[Cfg::kScalarAcc ? 1 : Cfg::kColsPerThread / 2];  // column pairs (2j, 2j+1)
+      float accf[Cfg::kScalarAcc ? Cfg::kColsPerThread : 1];
 #pragma unroll
-      for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) acc2[j] = 0ull;
+      for (int j = 0; j < (Cfg::kScalarAcc ? 1 : Cfg::kColsPerThread / 2); ++j) acc2[j] = 0ull;
+#pragma unroll
+      for (int j = 0; j < (Cfg::kScalarAcc ? Cfg::kColsPerThread : 1); ++j) accf[j] = 0.f;
 
       for (int kb0 = it.kb_begin; kb0 < it.kb_end && ok; kb0 += kScaleGroup) {
         // Scales of the next (up to) four K blocks: three 16-byte shared-memory loads, then the
@@ -864,7 +871,11 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             }
             const float s = (((gcol0 + ch * CC) >> 7) == jb0) ? s_lo[u] : s_hi[u];
             const unsigned long long s2 = pack2(s, s);
-            if constexpr (CC <= 32) {
+            if constexpr (Cfg::kScalarAcc) {
+              static_assert(!Cfg::kScalarAcc || CC == 32, "scalar accumulation is written for 32-column fetches");
+#pragma unroll
+              for (int j = 0; j < CC; ++j) accf[ch * CC + j] = fmaf(__uint_as_float(v[j]), s, accf[ch * CC + j]);
+            } else if constexpr (CC <= 32) {
 #pragma unroll
               for (int j = 0; j < CC / 2; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], s2);
             } else {
@@ -889,7 +900,13 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 
       float2 acc[Cfg::kColsPerThread / 2];
 #pragma unroll
-      for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) acc[j] = unpack2(acc2[j]);
+      for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) {
+        if constexpr (Cfg::kScalarAcc) {
+          acc[j] = make_float2(accf[2 * j], accf[2 * j + 1]);
+        } else {
+          acc[j] = unpack2(acc2[j]);
+        }
+      }
       const int col0 = it.n0 + col_base;  // first column of this thread inside (the shard of) c
       bool do_store = true;
       if (it.nsplit > 1) {
@@ -1146,9 +1163,10 @@ int tmem_bufs_in_use(int block_n, int stages) {
   return d < stages ? d : stages;
 }
 
-// Deepest ring that fits.
+// Deepest ring that fits. The 256-wide tiles stop at four stages: a fifth measured 5 % slower (their
+// promotion warps still spill a little, and local memory loses L1 to every extra stage).
 int max_stages_for(int block_n, int pair, int store_bufs) {
-  int s = kMaxStages;
+  int s = block_n == 256 ? 4 : kMaxStages;
   while (s > 2 && smem_bytes_for(block_n, s, pair, store_bufs) > kMaxSmem) --s;
   return s;
 }
@@ -1183,20 +1201,22 @@ struct WidthCost {
 };
 
 WidthCost width_cost(int bn, int pair) {
-  // CTA pairs: each CTA loads half of the B tile, which pays per K block at the 192-wide tile (5 % fewer
-  // clocks; long-K shapes gain 3-6 %, K <= 512 loses 2-5 % to the dearer tile turnaround). At the other
-  // widths pairs measured slower throughout.
-  if (pair && bn == 192) return {775.0, 3600.0, 8500.0, 1000.0};
+  // CTA pairs: each CTA loads half of the B tile, which pays per K block at the wide tiles (192: 5 % fewer
+  // clocks than single CTAs, 256: 20 % fewer; K <= 512 loses 2-5 % to the dearer tile turnaround). At 64 and
+  // 128 columns pairs measured slower throughout. Plans with a split-K tail measured about 7 % above this
+  // model, hence the larger constant.
+  if (pair && bn == 192) return {775.0, 3600.0, 12000.0, 1000.0};
+  if (pair && bn == 256) return {1010.0, 3600.0, 14000.0, 1500.0};
   switch (bn) {
     case 64: return {400.0, 1850.0, 6500.0, 750.0};
     case 128: return {585.0, 2500.0, 9000.0, 1100.0};
     case 192: return {815.0, 3300.0, 8500.0, 1000.0};
-    default: return {1330.0, 4400.0, 11000.0, 1500.0};
+    default: return {1260.0, 4400.0, 11000.0, 1500.0};
   }
 }
 
 // What a pair plan's cost is multiplied by, for the widths without a table of their own.
-double pair_penalty(int bn) { return bn == 192 ? 1.0 : (bn == 256 ? 1.35 : 1.04); }
+double pair_penalty(int bn) { return bn >= 192 ? 1.0 : 1.04; }
 
 struct Candidate {
   int bn, pair, split, full_tiles;
