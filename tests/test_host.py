@@ -114,8 +114,10 @@ def test_selector_is_pure_and_sane(built_library):
         tiles = -(-m // (p1.block_m * (2 if p1.cta_pair else 1))) * -(-n // p1.block_n)
         assert p1.tiles == tiles
         assert 1 <= p1.grid <= 148 and p1.grid <= tiles * p1.split_k * (2 if p1.cta_pair else 1)
+        # the size covers both this plan and the single-CTA plan that MN-major operands would get
         ws = pkg.workspace_bytes(m, n, k)
-        assert (ws == 0) == (p1.split_k == 1)
+        single = pkg.workspace_bytes(m, n, k, pkg.Plan(cta_pair=-1))
+        assert ws >= single and (ws == 0) == (p1.split_k == 1 and single == 0)
         if p1.split_k > 1:
             assert ws >= 4096 + (p1.tiles - p1.full_tiles) * p1.split_k * 128 * p1.block_n * 4
     with pytest.raises(Exception):
