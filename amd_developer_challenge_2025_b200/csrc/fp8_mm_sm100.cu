@@ -222,12 +222,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 }
 
 // Three-dimensional forms for grouped launches: the third coordinate is the group.
+template <bool PAIR>
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
-          dst),
-      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-      : "memory");
+  if constexpr (PAIR) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+  }
 }
 
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
@@ -648,8 +657,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             const uint32_t sa = smem_u32(ring + stage * Cfg::kStageBytes);
             // K-major: x = byte of K, y = matrix row. MN-major: x = matrix row (a multiple of 64), y = k.
             if (GENERIC && p.groups > 0) {
-              tma_load_3d(sa, &tmap_a, kb * kBlockK, a_row, it.group, fb);
-              tma_load_3d(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
+              tma_load_3d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, it.group, fb);
+              tma_load_3d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
             } else {
             if (!GENERIC || !p.a_mn) {
               tma_load_2d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, fb);
@@ -991,8 +1000,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           wg_bar_sync(half);
           if (wg_tid == 0) {
             if (GENERIC && p.groups > 0) {
-              tma_store_3d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols, it.m0,
-                           it.group);
+              tma_store_3d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
+                           it.m0 + static_cast<int>(cta_rank) * kBlockM, it.group);
             } else {
               tma_store_2d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
                            it.m0 + static_cast<int>(cta_rank) * kBlockM);
@@ -1202,16 +1211,16 @@ struct WidthCost {
 
 WidthCost width_cost(int bn, int pair) {
   // CTA pairs: each CTA loads half of the B tile, which pays per K block at the wide tiles (192: 5 % fewer
-  // clocks than single CTAs, 256: 20 % fewer; K <= 512 loses 2-5 % to the dearer tile turnaround). At 64 and
+  // clocks than single CTAs, 256: 12 % fewer; K <= 512 loses 2-5 % to the dearer tile turnaround). At 64 and
   // 128 columns pairs measured slower throughout. Plans with a split-K tail measured about 7 % above this
   // model, hence the larger constant.
   if (pair && bn == 192) return {775.0, 3600.0, 12000.0, 1000.0};
-  if (pair && bn == 256) return {1010.0, 3600.0, 14000.0, 1500.0};
+  if (pair && bn == 256) return {930.0, 3600.0, 14000.0, 1500.0};
   switch (bn) {
     case 64: return {400.0, 1850.0, 6500.0, 750.0};
     case 128: return {585.0, 2500.0, 9000.0, 1100.0};
     case 192: return {815.0, 3300.0, 8500.0, 1000.0};
-    default: return {1260.0, 4400.0, 11000.0, 1500.0};
+    default: return {1050.0, 4400.0, 11000.0, 1500.0};
   }
 }
 
@@ -1323,7 +1332,12 @@ typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap
 // generic: MN-major operands or a grouped launch (single CTAs only).
 KernelFn kernel_for(int block_n, int pair, bool generic) {
   if (generic) {
-    if (pair) return nullptr;
+    if (pair) {
+      // grouped launches on the two widths where pairs pay
+      if (block_n == 192) return fp8_mm_blockscaled_kernel<192, true, true>;
+      if (block_n == 256) return fp8_mm_blockscaled_kernel<256, true, true>;
+      return nullptr;
+    }
     switch (block_n) {
       case 64: return fp8_mm_blockscaled_kernel<64, false, true>;
       case 128: return fp8_mm_blockscaled_kernel<128, false, true>;
@@ -1492,11 +1506,11 @@ int launch(KernelFn fn, const b200_fp8_mm_plan& pl, const CUtensorMap& map_a, co
   // Opt every kernel in to the full 227 KiB of dynamic shared memory once per device.
   cudaError_t err = cudaSuccess;
   {
-    static unsigned char opted_in[64][12] = {};
+    static unsigned char opted_in[64][16] = {};
     int dev = 0;
     (void)cudaGetDevice(&dev);
     const bool generic = kp.groups > 0 || kp.a_mn || kp.b_mn;
-    const int slot = generic ? 8 + (pl.block_n / 64 - 1) : (pl.block_n / 64 - 1) * 2 + (pl.cta_pair ? 1 : 0);
+    const int slot = (generic ? 8 : 0) + (pl.block_n / 64 - 1) * 2 + (pl.cta_pair ? 1 : 0);
     if (dev < 0 || dev >= 64 || !opted_in[dev][slot]) {
       err = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kMaxSmem);
@@ -1540,8 +1554,7 @@ int run_grouped(const void* a, const void* b, const float* a_scale, const float*
   if (a == nullptr || b == nullptr || a_scale == nullptr || b_scale == nullptr || c == nullptr)
     return B200_FP8_MM_ERR_NULL;
   if (groups <= 0 || M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return B200_FP8_MM_ERR_SHAPE;
-  const int tiles_m = ceil_div(M, kBlockM);
-  if (static_cast<long long>(groups) * tiles_m > (1 << 20)) return B200_FP8_MM_ERR_SHAPE;
+  if (static_cast<long long>(groups) * ceil_div(M, kBlockM) > (1 << 20)) return B200_FP8_MM_ERR_SHAPE;
   if (lda < K || ldb < K || (lda % 16) != 0 || (ldb % 16) != 0 || ldc < N || (a_g % 16) != 0 || (b_g % 16) != 0 ||
       a_g < lda || b_g < ldb || c_g < ldc)
     return B200_FP8_MM_ERR_STRIDE;
@@ -1552,17 +1565,30 @@ int run_grouped(const void* a, const void* b, const float* a_scale, const float*
 
   b200_fp8_mm_plan forced;
   if (forced_in != nullptr) {
-    if (forced_in->cta_pair > 0 || forced_in->split_k > 1) return B200_FP8_MM_ERR_PLAN;
+    if (forced_in->split_k > 1) return B200_FP8_MM_ERR_PLAN;
     forced = *forced_in;
   } else {
     memset(&forced, 0, sizeof(forced));
   }
-  forced.cta_pair = -1;
   forced.split_k = 1;
+  // CTA pairs work on 256-row tiles inside each group: considered when a group's rows fill them to at
+  // least 7/8 (or when forced), and only at the widths that have a paired grouped kernel.
+  const int rows256 = ceil_div(M, 2 * kBlockM) * 2 * kBlockM;
+  const bool pair_fits = (rows256 - M) * 8 <= M;
+  if (forced.cta_pair == 0 && !pair_fits) forced.cta_pair = -1;
   b200_fp8_mm_plan pl;
-  choose_plan(groups * tiles_m * kBlockM, N, K, sm_count, &forced, &pl);
-  if (!plan_is_supported(pl, K / kBlockK) || pl.split_k != 1 || pl.cta_pair != 0) return B200_FP8_MM_ERR_PLAN;
-  KernelFn fn = kernel_for(pl.block_n, 0, true);
+  choose_plan(groups * rows256, N, K, sm_count, &forced, &pl);
+  if (pl.cta_pair && pl.block_n != 192 && pl.block_n != 256) {
+    if (forced_in != nullptr && forced_in->cta_pair > 0) return B200_FP8_MM_ERR_PLAN;
+    forced.cta_pair = -1;
+  }
+  if (!pl.cta_pair || forced.cta_pair < 0) {
+    forced.cta_pair = -1;
+    choose_plan(groups * ceil_div(M, kBlockM) * kBlockM, N, K, sm_count, &forced, &pl);
+  }
+  if (!plan_is_supported(pl, K / kBlockK) || pl.split_k != 1) return B200_FP8_MM_ERR_PLAN;
+  const int tiles_m = ceil_div(M, pl.cta_pair ? 2 * kBlockM : kBlockM);
+  KernelFn fn = kernel_for(pl.block_n, pl.cta_pair, true);
   if (fn == nullptr) return B200_FP8_MM_ERR_PLAN;
 
   CUtensorMap map_a, map_b, map_c;
@@ -1574,10 +1600,11 @@ int run_grouped(const void* a, const void* b, const float* a_scale, const float*
     memset(&map_c, 0, sizeof(map_c));
   }
   if (!encode_operand_map_3d(&map_a, a, groups, M, K, lda, a_g, kBlockM)) return B200_FP8_MM_ERR_DRIVER;
-  if (!encode_operand_map_3d(&map_b, b, groups, N, K, ldb, b_g, pl.block_n)) return B200_FP8_MM_ERR_DRIVER;
+  const int b_rows_per_cta = pl.cta_pair ? pl.block_n / 2 : pl.block_n;
+  if (!encode_operand_map_3d(&map_b, b, groups, N, K, ldb, b_g, b_rows_per_cta)) return B200_FP8_MM_ERR_DRIVER;
 
   const OperandLayout la = operand_layout(false, kBlockM);
-  const OperandLayout lb = operand_layout(false, pl.block_n);
+  const OperandLayout lb = operand_layout(false, b_rows_per_cta);
   KernelParams kp;
   memset(&kp, 0, sizeof(kp));
   kp.a_scale = a_scale;
@@ -1611,7 +1638,8 @@ int run_grouped(const void* a, const void* b, const float* a_scale, const float*
   kp.b_kstep = lb.kstep;
   kp.issuers = pl.block_n <= 128 ? 2 : 1;
   {
-    int g = (sm_count + kp.tiles_n / 2) / kp.tiles_n;
+    const int units = pl.cta_pair ? sm_count / 2 : sm_count;
+    int g = (units + kp.tiles_n / 2) / kp.tiles_n;
     if (g < 1) g = 1;
     if (g > 16) g = 16;
     kp.raster_group = g;
@@ -1625,7 +1653,11 @@ int run_grouped(const void* a, const void* b, const float* a_scale, const float*
   kp.c_g = c_g;
   pl.tiles = kp.full_tiles;
   pl.full_tiles = kp.full_tiles;
-  pl.grid = kp.full_tiles < sm_count ? kp.full_tiles : sm_count;
+  {
+    const int units = pl.cta_pair ? sm_count / 2 : sm_count;
+    const int used = kp.full_tiles < units ? kp.full_tiles : units;
+    pl.grid = pl.cta_pair ? 2 * used : used;
+  }
   return launch(fn, pl, map_a, map_b, map_c, kp, stream);
 }
 

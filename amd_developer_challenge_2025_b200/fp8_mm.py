@@ -213,7 +213,7 @@ def fp8_mm_grouped(a, b, a_scale, b_scale, c, m_valid=None, plan: Plan | None = 
         _check(m_valid.is_cuda and m_valid.device == dev and m_valid.dtype == torch.int32
                and tuple(m_valid.shape) == (g,) and m_valid.is_contiguous(), "m_valid must be a contiguous int32 CUDA tensor [G]")
     if plan is not None:
-        _check(plan.cta_pair <= 0 and plan.split_k <= 1, "grouped launches use whole tiles on single CTAs")
+        _check(plan.split_k <= 1, "grouped launches use whole tiles (no split-K)")
     if dev.index != torch.cuda.current_device():
         with torch.cuda.device(dev):
             return fp8_mm_grouped(a, b, a_scale, b_scale, c, m_valid, plan, check)

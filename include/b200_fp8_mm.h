@@ -160,8 +160,9 @@ int b200_fp8_mm_strided(const void* a, const void* b, const float* a_scale, cons
  *           (clamped to [0, M]). Tiles past it are skipped, rows past it are not written. The
  *           array is read by the kernel, so it may be produced on the stream just before.
  *  lda, ldb, a_g, b_g multiples of 16; a and b 16-byte aligned; K a multiple of 128
- *  forced   NULL, or a plan (block_n, stages, store_bufs are read); every tile is whole:
- *           split_k > 1 or cta_pair = 1 give B200_FP8_MM_ERR_PLAN
+ *  forced   NULL, or a plan (block_n, cta_pair, stages, store_bufs are read); every tile is whole:
+ *           split_k > 1 gives B200_FP8_MM_ERR_PLAN. CTA pairs (256-row tiles inside each group)
+ *           exist for block_n 192 and 256; they are chosen when M fills 256-row tiles to 7/8
  *
  * Needs no workspace. Asynchronous; inputs are never written.
  */

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import amd_developer_challenge_2025_b200 as pkg
-from amd_developer_challenge_2025_b200.fp8_mm import Plan, check_device_status
+from amd_developer_challenge_2025_b200.fp8_mm import Fp8MmError, Plan, check_device_status
 from oracle import fp8_mm_oracle as oracle
 
 pytestmark = pytest.mark.gpu
@@ -34,12 +34,12 @@ def test_groups_against_oracle(g, m, n, k):
         assert_close(c[i], oracle.dequant_matmul(a[i], b[i], a_s[i], b_s[i]), f"group {i} of {g}x{m}x{n}x{k}")
 
 
-@pytest.mark.parametrize("bn", [64, 128, 192, 256])
+@pytest.mark.parametrize("bn,pair", [(64, -1), (128, -1), (192, -1), (256, -1), (192, 1), (256, 1)])
 @pytest.mark.parametrize("store_bufs", [-1, 1, 2])
-def test_every_width_equals_separate_launches(bn, store_bufs):
+def test_every_width_equals_separate_launches(bn, pair, store_bufs):
     g, m, n, k = 3, 392, 840, 768
     a, b, a_s, b_s, c = grouped_inputs(g, m, n, k, 5)
-    plan = Plan(block_n=bn, cta_pair=-1, split_k=1, store_bufs=store_bufs)
+    plan = Plan(block_n=bn, cta_pair=pair, split_k=1, store_bufs=store_bufs)
     pkg.fp8_mm_grouped(a, b, a_s, b_s, c, plan=plan)
     check_device_status()
     for i in range(g):
@@ -57,7 +57,8 @@ def test_valid_rows_per_group_are_respected():
     a, b, a_s, b_s, c = grouped_inputs(g, m, n, k, 9)
     valid = [384, 0, 17, 256, 300]
     mv = torch.tensor(valid, dtype=torch.int32, device="cuda")
-    for plan in (None, Plan(block_n=128, cta_pair=-1, store_bufs=-1), Plan(block_n=64, cta_pair=-1, store_bufs=2)):
+    for plan in (None, Plan(block_n=128, cta_pair=-1, store_bufs=-1), Plan(block_n=64, cta_pair=-1, store_bufs=2),
+                 Plan(block_n=192, cta_pair=1), Plan(block_n=256, cta_pair=1, store_bufs=-1)):
         c.fill_(float("nan"))
         pkg.fp8_mm_grouped(a, b, a_s, b_s, c, m_valid=mv, plan=plan)
         check_device_status()
@@ -104,6 +105,8 @@ def test_grouped_errors():
         pkg.fp8_mm_grouped(a[0], b, a_s, b_s, c)                               # a not 3-D
     with pytest.raises(ValueError):
         pkg.fp8_mm_grouped(a, b, a_s, b_s, c, plan=Plan(split_k=2))            # no split-K in grouped launches
+    with pytest.raises(Fp8MmError):
+        pkg.fp8_mm_grouped(a, b, a_s, b_s, c, plan=Plan(block_n=128, cta_pair=1))  # no paired kernel at this width
     with pytest.raises(ValueError):
         pkg.fp8_mm_grouped(a, b, a_s, b_s, c, m_valid=torch.zeros(2, dtype=torch.int64, device="cuda"))
     check_device_status()
