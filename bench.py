@@ -35,8 +35,8 @@ NOMINAL_FP8_TFLOPS = 4500.0
 FALLBACK_BF16_TFLOPS = 1590.0
 L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes of one launch of the headline GEMM on one GPU, from the ncu capture summarised in
-# profiles/fp8_mm_blockscaled_kernel_192_pair_headline_ncu_full.md (106.6 MB read + 61.3 MB written).
-HEADLINE_DRAM_BYTES = 167_850_000
+# profiles/fp8_mm_blockscaled_kernel_256_pair_headline_ncu_full.md (113.7 MB read + 57.4 MB written).
+HEADLINE_DRAM_BYTES = 171_100_000
 SWEEP_NK = ((1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
             (512, 7168), (4096, 512))
 SWEEP_M = (512, 2048, 8192, 16384)
