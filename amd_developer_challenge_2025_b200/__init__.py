@@ -6,7 +6,7 @@ hand-written sm_100a CUDA kernels in ``lib/libb200fp8mm.so`` reached through a C
 (``include/b200_fp8_mm.h``). There is no CPU or library fallback: if the shared
 library is missing the import of ``_lib`` raises.
 """
-from .fp8_mm import Plan, describe, fp8_mm, fp8_mm_grouped, fp8_mm_host, workspace_bytes  # noqa: F401
+from .fp8_mm import Plan, describe, estimate_clocks, fp8_mm, fp8_mm_grouped, fp8_mm_host, workspace_bytes  # noqa: F401
 from .inputs import make_inputs  # noqa: F401
-from .sharding import ShardSpec, shard_inputs, shard_spec  # noqa: F401
+from .sharding import GridSpec, ShardSpec, choose_grid, grid_inputs, grid_spec, shard_inputs, shard_spec  # noqa: F401
 from .submission import custom_kernel  # noqa: F401

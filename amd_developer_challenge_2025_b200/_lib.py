@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # B200_FP8_MM_LIB selects another build of the same library (e.g. one made with extra nvcc flags).
 LIB_PATH = os.environ.get("B200_FP8_MM_LIB") or os.path.join(HERE, "lib", "libb200fp8mm.so")
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 # Every symbol include/b200_fp8_mm.h declares.
 EXPORTS = (
@@ -23,6 +23,7 @@ EXPORTS = (
     "b200_fp8_mm_workspace_bytes",
     "b200_fp8_mm_plan_workspace_bytes",
     "b200_fp8_mm_describe",
+    "b200_fp8_mm_estimate_clocks",
     "b200_fp8_mm_strerror",
     "b200_fp8_mm_abi_version",
 )
@@ -88,6 +89,8 @@ def load() -> ctypes.CDLL:
     lib.b200_fp8_mm_plan_workspace_bytes.restype = ctypes.c_size_t
     lib.b200_fp8_mm_describe.argtypes = [ctypes.c_int] * 5 + [ctypes.POINTER(CPlan)]
     lib.b200_fp8_mm_describe.restype = ctypes.c_int
+    lib.b200_fp8_mm_estimate_clocks.argtypes = [ctypes.c_int] * 4
+    lib.b200_fp8_mm_estimate_clocks.restype = ctypes.c_double
     lib.b200_fp8_mm_strerror.argtypes = [ctypes.c_int]
     lib.b200_fp8_mm_strerror.restype = ctypes.c_char_p
     lib.b200_fp8_mm_abi_version.argtypes = []

@@ -1272,7 +1272,7 @@ Candidate evaluate(int M, int N, int kblocks, int sm_count, int bn, int pair, in
   return best;
 }
 
-void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forced, b200_fp8_mm_plan* out) {
+double choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forced, b200_fp8_mm_plan* out) {
   const int kblocks = K / kBlockK;
   const int f_bn = (forced && forced->block_n) ? forced->block_n : 0;
   const int f_pair = (forced && forced->cta_pair) ? (forced->cta_pair > 0 ? 1 : 0) : -1;  // -1: choose
@@ -1312,6 +1312,7 @@ void choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* forc
   out->grid = pair ? 2 * used : used;
   out->store_bufs = store_bufs;
   out->smem_bytes = valid_block_n(bn) ? smem_bytes_for(bn, stages, pair, store_bufs) : 0;
+  return best.cost;
 }
 
 bool plan_is_supported(const b200_fp8_mm_plan& pl, int kblocks) {
@@ -1788,6 +1789,12 @@ int b200_fp8_mm_describe(int M, int N, int K, int n_phase, int sm_count, b200_fp
   return B200_FP8_MM_OK;
 }
 
+double b200_fp8_mm_estimate_clocks(int M, int N, int K, int sm_count) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return -1.0;
+  b200_fp8_mm_plan pl;
+  return choose_plan(M, N, K, sm_count > 0 ? sm_count : 148, nullptr, &pl);
+}
+
 const char* b200_fp8_mm_strerror(int code) {
   switch (code) {
     case B200_FP8_MM_OK: return "ok";
@@ -1808,6 +1815,6 @@ const char* b200_fp8_mm_strerror(int code) {
   }
 }
 
-int b200_fp8_mm_abi_version(void) { return 5; }
+int b200_fp8_mm_abi_version(void) { return 6; }
 
 }  // extern "C"

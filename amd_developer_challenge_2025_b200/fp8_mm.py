@@ -56,6 +56,14 @@ def describe(m: int, n: int, k: int, n_phase: int = 0, sm_count: int = 0) -> Pla
     return Plan.from_c(out)
 
 
+def estimate_clocks(m: int, n: int, k: int, sm_count: int = 0) -> float:
+    """The selector's cost estimate (SM clocks) for the plan it would pick; host arithmetic only."""
+    v = float(_lib.load().b200_fp8_mm_estimate_clocks(m, n, k, sm_count))
+    if v < 0:
+        raise Fp8MmError(2)
+    return v
+
+
 def workspace_bytes(m: int, n: int, k: int, plan: Plan | None = None) -> int:
     lib = _lib.load()
     if plan is None:

@@ -52,3 +52,86 @@ def shard_spec(n: int, world: int, rank: int) -> ShardSpec:
 def shard_inputs(b, b_scale, spec: ShardSpec):
     """The (b, b_scale) rows rank `spec.rank` holds. Views; call .contiguous() to own them."""
     return b[spec.col_begin : spec.col_end], b_scale[spec.scale_row_begin : spec.scale_row_end]
+
+
+# ---------------------------------------------------------------------------------------------
+# Two-dimensional sharding: a grid of row blocks x column blocks
+# ---------------------------------------------------------------------------------------------
+# Every output tile is independent, so the ranks may also cut c along M: rank (i, j) of a
+# grid_m x grid_n grid owns row block i (its rows of a and a_scale) and column block j (as above).
+# Still no data-path collective. Which grid is best depends on how the per-rank problem fills the
+# SMs: 8192 x 4608 x 7168 over 8 GPUs as 1 x 8 leaves each GPU 2.2 waves of work, as 4 x 2 each
+# GPU gets 2048 x 2304 = 72 pair tiles of 256 x 256 on 74 SM pairs, one wave.
+
+
+@dataclass(frozen=True)
+class GridSpec:
+    rank: int
+    world: int
+    grid_m: int
+    grid_n: int
+    row_begin: int
+    row_end: int
+    cols: ShardSpec  # the column block, as for one-dimensional sharding over grid_n ranks
+
+    @property
+    def m_local(self) -> int:
+        return self.row_end - self.row_begin
+
+    @property
+    def n_local(self) -> int:
+        return self.cols.n_local
+
+    @property
+    def n_phase(self) -> int:
+        return self.cols.n_phase
+
+
+def _row_range(m: int, parts: int, index: int):
+    """Rows dealt in units of 128 (one tile row); the first blocks get one unit more when uneven."""
+    units = -(-m // 128)
+    if units < parts:
+        raise ValueError(f"M={m} has only {units} row blocks for {parts} row shards")
+    base, extra = divmod(units, parts)
+    u0 = index * base + min(index, extra)
+    u1 = u0 + base + (1 if index < extra else 0)
+    return u0 * 128, min(u1 * 128, m)
+
+
+def grid_spec(m: int, n: int, world: int, rank: int, grid_m: int, grid_n: int) -> GridSpec:
+    """The block of rank `rank` in a grid_m x grid_n grid (rank = i * grid_n + j)."""
+    if grid_m * grid_n != world or not (0 <= rank < world):
+        raise ValueError("grid does not match world, or bad rank")
+    i, j = divmod(rank, grid_n)
+    r0, r1 = _row_range(m, grid_m, i)
+    return GridSpec(rank, world, grid_m, grid_n, r0, r1, shard_spec(n, grid_n, j))
+
+
+def choose_grid(m: int, n: int, k: int, world: int, estimate=None):
+    """(grid_m, grid_n) with grid_m * grid_n = world that minimises the slowest rank's estimated time.
+    `estimate(m, n, k) -> cost` defaults to the library's own model (b200_fp8_mm_estimate_clocks);
+    ties go to the grid with fewer row shards (a is then replicated rather than cut, as in the
+    one-dimensional scheme)."""
+    if estimate is None:
+        from .fp8_mm import estimate_clocks as estimate
+    best = None
+    for gm in range(1, world + 1):
+        if world % gm:
+            continue
+        gn = world // gm
+        try:
+            worst = max(estimate(s.m_local, s.n_local, k)
+                        for s in (grid_spec(m, n, world, r, gm, gn) for r in range(world)))
+        except ValueError:
+            continue
+        if best is None or worst < best[0] * (1 - 1e-9):
+            best = (worst, gm, gn)
+    if best is None:
+        raise ValueError(f"no grid of {world} ranks fits M={m}, N={n}")
+    return best[1], best[2]
+
+
+def grid_inputs(a, b, a_scale, b_scale, spec: GridSpec):
+    """The (a, b, a_scale, b_scale) blocks rank `spec.rank` holds. Views."""
+    bb, bs = shard_inputs(b, b_scale, spec.cols)
+    return a[spec.row_begin : spec.row_end], bb, a_scale[spec.row_begin : spec.row_end], bs

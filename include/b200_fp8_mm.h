@@ -225,6 +225,11 @@ size_t b200_fp8_mm_plan_workspace_bytes(int M, int N, int K, const b200_fp8_mm_p
  * sm_count SMs (0 = 148). Pure host arithmetic; needs no GPU. */
 int b200_fp8_mm_describe(int M, int N, int K, int n_phase, int sm_count, b200_fp8_mm_plan* out);
 
+/* The selector's own cost estimate for the plan it would pick, in SM clocks (about 1.9 GHz);
+ * negative for a bad shape. Pure host arithmetic. Used to compare ways of cutting one problem into
+ * per-GPU pieces; it is a model fitted to measurements, good to a few percent, not a promise. */
+double b200_fp8_mm_estimate_clocks(int M, int N, int K, int sm_count);
+
 /* Text for a return code. */
 const char* b200_fp8_mm_strerror(int code);
 

@@ -206,6 +206,21 @@ def test_sharded_equals_whole_at_4608(world):
     assert_close(got, c.cpu(), "sharded vs whole")
 
 
+@pytest.mark.parametrize("gm,gn", [(2, 2), (4, 2), (2, 1)])
+def test_grid_sharded_equals_whole(gm, gn):
+    """Row x column blocks of c computed separately (as the ranks of a multi-GPU run do) against the oracle."""
+    m, n, k = 1152, 1216, 512
+    a, b, a_s, b_s, _ = cuda_inputs(m, n, k, 55)
+    got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for r in range(gm * gn):
+        s = pkg.grid_spec(m, n, gm * gn, r, gm, gn)
+        aa, bb, aas, bs = pkg.grid_inputs(a, b, a_s, b_s, s)
+        cc = torch.empty(s.m_local, s.n_local, dtype=torch.bfloat16, device="cuda")
+        run(aa, bb, aas, bs, cc, n_phase=s.n_phase)   # views: row-sliced a and b need no copy
+        got[s.row_begin:s.row_end, s.cols.col_begin:s.cols.col_end] = cc
+    assert_close(got, oracle.dequant_matmul(a, b, a_s, b_s), f"grid {gm}x{gn}")
+
+
 def test_strided_operands_and_output():
     """Row-padded a/b, M-major (transposed-storage) scales, and c as a column slice of a wider buffer."""
     m, n, k = 300, 576, 768

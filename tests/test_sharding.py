@@ -9,7 +9,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from amd_developer_challenge_2025_b200.inputs import make_inputs
-from amd_developer_challenge_2025_b200.sharding import shard_inputs, shard_spec
+from amd_developer_challenge_2025_b200.sharding import choose_grid, grid_inputs, grid_spec, shard_inputs, shard_spec
 from oracle import fp8_mm_oracle as oracle
 
 
@@ -54,6 +54,45 @@ def test_shards_tile_the_columns_and_reproduce_the_full_result(world):
         assert bs.shape[0] == (s.n_local + s.n_phase + 127) // 128
         cols.append(oracle.dequant_matmul(a, bb, a_s, bs, s.n_phase))
     assert torch.equal(torch.cat(cols, dim=1).view(torch.int16), full.view(torch.int16))
+
+
+@pytest.mark.parametrize("gm,gn", [(1, 4), (2, 2), (4, 1), (3, 2), (2, 4)])
+def test_grid_blocks_tile_c_and_reproduce_the_full_result(gm, gn):
+    m, n, k = 520, 576, 256   # 5 row blocks (the last one short), 9 column units
+    a, b, a_s, b_s, _ = make_inputs(m, n, k, seed=33)
+    full = oracle.dequant_matmul(a, b, a_s, b_s)
+    got = torch.full((m, n), float("nan"), dtype=torch.bfloat16)
+    covered = torch.zeros(m, n, dtype=torch.int32)
+    for r in range(gm * gn):
+        s = grid_spec(m, n, gm * gn, r, gm, gn)
+        aa, bb, aas, bs = grid_inputs(a, b, a_s, b_s, s)
+        assert aa.shape[0] == s.m_local and bb.shape[0] == s.n_local and s.row_begin % 128 == 0
+        got[s.row_begin:s.row_end, s.cols.col_begin:s.cols.col_end] = oracle.dequant_matmul(aa, bb, aas, bs, s.n_phase)
+        covered[s.row_begin:s.row_end, s.cols.col_begin:s.cols.col_end] += 1
+    assert bool((covered == 1).all())
+    assert torch.equal(got.view(torch.int16), full.view(torch.int16))
+
+
+def test_choose_grid_minimises_the_slowest_rank():
+    # a cost that only counts whole waves of 128 x 128 tiles on 4 "SMs"
+    waves = lambda m, n, k: -(-(-(-m // 128) * -(-n // 128)) // 4) * k
+    assert choose_grid(1024, 256, 128, 4, estimate=waves) in ((2, 2), (4, 1))   # 4 tiles per rank either way
+    assert choose_grid(128, 4096, 128, 4, estimate=waves) == (1, 4)            # one row block: columns only
+    assert choose_grid(4096, 64, 128, 4, estimate=waves) == (4, 1)             # one column unit: rows only
+    with pytest.raises(ValueError):
+        choose_grid(128, 64, 128, 4, estimate=waves)                           # nothing to cut four ways
+    with pytest.raises(ValueError):
+        grid_spec(1024, 1024, 4, 0, 3, 2)
+
+
+def test_choose_grid_with_the_library_model(built_library):
+    # the headline GEMM over 8 GPUs: 4 x 2 gives every GPU one wave of 256 x 256 pair tiles
+    assert choose_grid(8192, 4608, 7168, 8) == (4, 2)
+    assert choose_grid(8192, 4608, 7168, 1) == (1, 1)
+    import amd_developer_challenge_2025_b200 as pkg
+    assert pkg.estimate_clocks(8192, 4608, 7168) > pkg.estimate_clocks(2048, 2304, 7168) * 7
+    with pytest.raises(Exception):
+        pkg.estimate_clocks(128, 128, 100)
 
 
 def _free_port():
