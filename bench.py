@@ -249,7 +249,7 @@ def run_ours(args):
     # The ranks form a grid of row blocks x column blocks of c (no collective either way); the grid is the one
     # whose slowest rank the library's cost model rates fastest (8 GPUs: 4 x 2, one wave of 256 x 256 pair
     # tiles per GPU, where 1 x 8 would leave each GPU 2.2 waves of narrower tiles).
-    grid_m, grid_n = pkg.choose_grid(m, n, k, world)
+    grid_m, grid_n = (tuple(int(x) for x in args.grid.split("x")) if args.grid else pkg.choose_grid(m, n, k, world))
     spec = pkg.grid_spec(m, n, world, rank, grid_m, grid_n)
     m_full, m = m, spec.m_local
     n_loc = spec.n_local
@@ -446,6 +446,7 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-shape sweep (N=1 only)")
     ap.add_argument("--shape", default="", help="M,N,K of another workload (for small profiler captures)")
+    ap.add_argument("--grid", default="", help="ROWSxCOLS grid of the ranks (default: the cost model's choice)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
