@@ -34,8 +34,8 @@ UNIT = "TFLOP/s"
 NOMINAL_FP8_TFLOPS = 4500.0
 FALLBACK_BF16_TFLOPS = 1590.0
 L2_BYTES = 126 * 1024 * 1024
-# DRAM bytes of one launch of the headline GEMM on one GPU, from the ncu capture summarised in
-# profiles/fp8_mm_blockscaled_kernel_256_pair_headline_ncu_full.md (113.7 MB read + 57.4 MB written).
+# DRAM bytes of one launch of the headline GEMM on one GPU, from an ncu capture of that launch
+# (dram__bytes_read.sum 113.7 MB + dram__bytes_write.sum 57.4 MB).
 HEADLINE_DRAM_BYTES = 171_100_000
 SWEEP_NK = ((1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
             (512, 7168), (4096, 512))
