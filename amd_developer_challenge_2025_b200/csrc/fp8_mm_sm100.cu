@@ -506,6 +506,9 @@ struct TileCfg {
   // thread the packed form spills (the pairs want aligned 64-bit registers next to a 32-register landing
   // area); scalars fit, and the 256-wide pair plan went from 442 to 262 us on the headline GEMM.
   static constexpr bool kScalarAcc = (BN == 256);
+  // At BN=256 the first 64 of a thread's 128 columns stay packed (no spill, 1 % faster than all scalar);
+  // 96 packed columns spill again.
+  static constexpr int kPackedCols = kScalarAcc ? 64 : kColsPerThread;
   // Narrow tiles: the promotion warps probe the next K block's barrier (non-blocking) right after they
   // release a buffer, so the answer arrives during the fmas and the blocking wait is skipped when the
   // block is already there. Measured -3 % at 64 and 128 columns, 0 at 256, +2.6 % on 192-wide pairs.
@@ -846,12 +849,14 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       const int jb0 = gcol0 >> 7;
       const int bi0 = jb0 - ((it.n0 + p.n_phase) >> 7);
 
-      unsigned long long acc2[Cfg::kScalarAcc ? 1 : Cfg::kColsPerThread / 2];  // column pairs (2j, 2j+1)
-      float accf[Cfg::kScalarAcc ? Cfg::kColsPerThread : 1];
+      constexpr int kPackedCols = Cfg::kPackedCols;
+      constexpr int kScalarCols = Cfg::kColsPerThread - kPackedCols;
+      unsigned long long acc2[kPackedCols / 2 > 0 ? kPackedCols / 2 : 1];
+      float accf[kScalarCols > 0 ? kScalarCols : 1];
 #pragma unroll
-      for (int j = 0; j < (Cfg::kScalarAcc ? 1 : Cfg::kColsPerThread / 2); ++j) acc2[j] = 0ull;
+      for (int j = 0; j < (kPackedCols / 2 > 0 ? kPackedCols / 2 : 1); ++j) acc2[j] = 0ull;
 #pragma unroll
-      for (int j = 0; j < (Cfg::kScalarAcc ? Cfg::kColsPerThread : 1); ++j) accf[j] = 0.f;
+      for (int j = 0; j < (kScalarCols > 0 ? kScalarCols : 1); ++j) accf[j] = 0.f;
 
       for (int kb0 = it.kb_begin; kb0 < it.kb_end && ok; kb0 += kScaleGroup) {
         // Scales of the next (up to) four K blocks: three 16-byte shared-memory loads, then the
@@ -909,9 +914,14 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             const float s = (((gcol0 + ch * CC) >> 7) == jb0) ? s_lo[u] : s_hi[u];
             const unsigned long long s2 = pack2(s, s);
             if constexpr (Cfg::kScalarAcc) {
-              static_assert(!Cfg::kScalarAcc || CC == 32, "scalar accumulation is written for 32-column fetches");
+              if (ch * CC < kPackedCols) {
 #pragma unroll
-              for (int j = 0; j < CC; ++j) accf[ch * CC + j] = fmaf(__uint_as_float(v[j]), s, accf[ch * CC + j]);
+                for (int j = 0; j < CC / 2; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], s2);
+              } else {
+#pragma unroll
+                for (int j = 0; j < CC; ++j)
+                  accf[ch * CC - kPackedCols + j] = fmaf(__uint_as_float(v[j]), s, accf[ch * CC - kPackedCols + j]);
+              }
             } else if constexpr (CC <= 32) {
 #pragma unroll
               for (int j = 0; j < CC / 2; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], s2);
@@ -939,7 +949,11 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
       for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) {
         if constexpr (Cfg::kScalarAcc) {
-          acc[j] = make_float2(accf[2 * j], accf[2 * j + 1]);
+          if (2 * j < kPackedCols) {
+            acc[j] = unpack2(acc2[j]);
+          } else {
+            acc[j] = make_float2(accf[2 * j - kPackedCols], accf[2 * j + 1 - kPackedCols]);
+          }
         } else {
           acc[j] = unpack2(acc2[j]);
         }
