@@ -1,8 +1,7 @@
 """Builds the plain-C oracle into oracle/_build/libfp8mm_oracle.so with gcc.
 
-There is no oracle/_ref: the reference's implementation of this path is HIP C++ for
-gfx942 embedded in Python strings and needs ROCm's hipcc and headers, so it cannot be
-compiled with gcc or nvcc from its own sources."""
+(The reference's own dequantise kernels are compiled by build_ref.py into oracle/_ref/. Its
+GEMM kernels are HIP C++ for gfx942 built on MFMA builtins and cannot be compiled here.)"""
 from __future__ import annotations
 
 import os

@@ -1,7 +1,7 @@
 /*
  * Plain-C restatement of the FP8 block-scaled GEMM, independent of torch: it carries
- * its own e4m3fn decoder. Test infrastructure only (see oracle/fp8_mm_oracle.py for
- * the "parity unpinned" statement); nothing in the product links it.
+ * its own e4m3fn decoder. Test infrastructure only (oracle/fp8_mm_oracle.py says
+ * what it is pinned to); nothing in the product links it.
  *
  * fp8mm_oracle_dequant  follows 1-amd-fp8-mm/0-amd-fp8-mm-new-begins.py:17-25, 34-42, 85-89:
  *                       dequantise a and b to fp32, then a plain fp32 dot product per output.

@@ -1,11 +1,22 @@
 """CPU oracle for the FP8 block-scaled GEMM (test infrastructure, not product code).
 
-PARITY UNPINNED BY THE REFERENCE: the reference ships no golden vectors, tests or
-fixtures for this path, and its sources (HIP for gfx942, plus a `task` module that is
-not part of the project) can be neither compiled nor imported on a CUDA machine. This
-file restates the reference's dequantise-then-matmul script and is pinned instead to
-(a) an independent plain-C restatement with its own e4m3fn decoder
-(oracle/fp8_mm_oracle.c) and (b) committed fixtures under tests/golden/.
+Pinning. The reference ships no golden vectors, tests or fixtures for this path, but the two
+dequantise kernels of its dequantise-then-matmul script are plain loops, and oracle/build_ref.py
+compiles them UNMODIFIED for the host (oracle/_ref, behind oracle/ref_oracle.py). Against them:
+
+* ``dequant_a`` / ``dequant_b`` are bit-for-bit equal to the reference's ``dqa_kernel`` /
+  ``dqb_kernel`` run on the reference's own [k][m] / [k][n] / [k/128][m] / [k/128][ceil(n/128)]
+  storage (tests/test_oracle.py), and the committed fixtures under tests/golden/ are those
+  kernels' outputs (tests/golden/make_golden.py).
+* What stays unpinned: (1) the byte decode. The reference reads its bytes as e4m3fnuz; the
+  contract this repository is built to fixes e4m3fn on both sides, so the shim that compiles the
+  reference's kernels gives their ``(float)src_val`` an e4m3fn decode (checked against torch's for
+  all 256 codes). (2) The order in which the final ``a_fp32.T @ b_fp32`` adds its K products: a
+  BLAS property on either side, worth about 1e-6 relative in fp32, far below the bf16 output's
+  resolution.
+
+A second, independent pin: a plain-C restatement with its own e4m3fn decoder
+(oracle/fp8_mm_oracle.c).
 
 Functions and the reference lines they follow:
 

@@ -1,14 +1,16 @@
-"""Generates tests/golden/*.npz: small seeded problems with the outputs of the torch CPU
-restatement of the reference's dequantise-then-matmul script
-(1-amd-fp8-mm/0-amd-fp8-mm-new-begins.py:17-49, 85-89) plus the e4m3fn decode table.
+"""Generates tests/golden/*.npz from the REFERENCE'S OWN dequantise kernels compiled for the host.
 
-The reference itself cannot be imported or compiled on a CUDA machine (HIP for gfx942 and a
-`task` module that is not part of the project), and it holds no golden vectors, so these
-fixtures pin the oracle against regressions and against the independent C restatement; they
-are not outputs of the reference's own code.
+Each fixture is a small seeded problem plus what the reference's code made of it:
+`dqa_kernel` / `dqb_kernel` (1-amd-fp8-mm/0-amd-fp8-mm-new-begins.py:17-25, 34-42), compiled
+unmodified by oracle/build_ref.py, give the dequantised operands (stored as SHA-256 digests of
+their fp32 bytes, in the reference's [k][m] / [k][n] storage), and the script's
+`a_fp32.T @ b_fp32` (same file, 85-89) as a torch CPU matmul gives `c_fp32`. A column shard
+(`n_phase` > 0) is cut out of the whole problem's result, since the reference has no shards.
 
+Needs the reference checkout (see oracle/build_ref.py); the fixtures it writes travel without it.
 Run from the repository root:  python tests/golden/make_golden.py
 """
+import hashlib
 import os
 import sys
 
@@ -19,7 +21,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 sys.path.insert(0, ROOT)
 
 from amd_developer_challenge_2025_b200.inputs import make_inputs  # noqa: E402
-from oracle import fp8_mm_oracle as oracle  # noqa: E402
+from oracle import ref_oracle  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -33,25 +35,31 @@ CASES = [
 ]
 
 
+def digest(t: torch.Tensor) -> np.ndarray:
+    return np.frombuffer(hashlib.sha256(t.contiguous().numpy().tobytes()).digest(), dtype=np.uint8).copy()
+
+
 def main():
     torch.set_num_threads(1)
+    if ref_oracle.build_ref.reference_source() is None:
+        raise SystemExit("the reference checkout is needed to regenerate the fixtures")
     for name, m, n, k, seed, phase in CASES:
-        if phase:
-            # build a wider problem and cut the shard out of it, as the multi-GPU path does
-            a, b_full, a_s, bs_full, _ = make_inputs(m, n + phase, k, seed)
-            b = b_full[phase:].contiguous()
-            b_s = bs_full
-        else:
-            a, b, a_s, b_s, _ = make_inputs(m, n, k, seed)
-        c32 = oracle.dequant_matmul_fp32(a, b, a_s, b_s, phase)
+        # a shard is generated as the wider problem it is cut from, as the multi-GPU path does
+        a, b_full, a_s, bs_full, _ = make_inputs(m, n + phase, k, seed)
+        a_km = ref_oracle.dequant_a_km(a, a_s)              # [K, M]
+        b_kn = ref_oracle.dequant_b_kn(b_full, bs_full)     # [K, N + phase]
+        c32 = (a_km.T @ b_kn)[:, phase:].contiguous()
+        b = b_full[phase:].contiguous()
         c16 = c32.to(torch.bfloat16)
         np.savez_compressed(
             os.path.join(HERE, name + ".npz"),
             a=a.view(torch.uint8).numpy(), b=b.view(torch.uint8).numpy(),
-            a_scale=a_s.numpy(), b_scale=b_s.numpy(),
+            a_scale=a_s.numpy(), b_scale=bs_full.numpy(),
             c_fp32=c32.numpy(), c_bf16_bits=c16.view(torch.int16).numpy(),
+            dq_a_km_sha256=digest(a_km), dq_b_kn_sha256=digest(b_kn[:, phase:]),
             meta=np.array([m, n, k, seed, phase], dtype=np.int64),
         )
+    # the decode table comes from torch's e4m3fn decoder (a third party to both the oracle and the shim)
     table = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy()
     np.save(os.path.join(HERE, "e4m3fn_table.npy"), table)
 

@@ -1,6 +1,8 @@
-"""CPU tests of the oracle: against the committed fixtures, against the independent plain-C
+"""CPU tests of the oracle: against the reference's own dequantise kernels compiled for the host
+(oracle/_ref), against the committed fixtures those kernels produced, against the independent plain-C
 restatement, and the two summation orders against each other within the contract's tolerance."""
 import glob
+import hashlib
 import os
 
 import numpy as np
@@ -10,6 +12,10 @@ import torch
 from amd_developer_challenge_2025_b200.inputs import make_inputs
 from oracle import c_oracle
 from oracle import fp8_mm_oracle as oracle
+from oracle import ref_oracle
+
+needs_ref = pytest.mark.skipif(not ref_oracle.available(),
+                               reason="neither the reference checkout nor a prebuilt oracle/_ref is present")
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 CASES = sorted(glob.glob(os.path.join(GOLDEN, "*.npz")))
@@ -27,6 +33,10 @@ def load_case(path):
     return a, b, a_s, b_s, c32, c16, (m, n, k, seed, phase)
 
 
+def sha(t: torch.Tensor) -> bytes:
+    return hashlib.sha256(t.contiguous().numpy().tobytes()).digest()
+
+
 def test_fixtures_exist():
     assert len(CASES) >= 5
 
@@ -42,6 +52,60 @@ def test_e4m3fn_decode_table_all_256_codes():
     # e4m3fn landmarks: max 448, smallest subnormal 2^-9, NaN only at 0x7f / 0xff
     assert want[0x7E] == 448.0 and want[0x01] == 2.0 ** -9 and want[0x38] == 1.0
     assert np.isnan(want[0x7F]) and np.isnan(want[0xFF]) and np.isnan(want).sum() == 2
+
+
+@needs_ref
+def test_reference_shim_decodes_e4m3fn_like_torch():
+    """The float conversion given to the reference's `(float)src_val` is torch's e4m3fn decode, all 256 codes."""
+    want = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).float().numpy()
+    got = ref_oracle.decode_table()
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.array_equal(got[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
+
+
+# Beside the fixtures: N=576 (five b_scale rows, the last one half used), a ragged everything, and
+# one problem at config 0's K.
+REF_SHAPES = [(40, 576, 384, 13), (7, 130, 128, 21), (65, 577, 256, 22), (16, 1536, 7168, 23)]
+
+
+@needs_ref
+@pytest.mark.parametrize("m,n,k,seed", REF_SHAPES)
+def test_dequantise_equals_reference_kernels_bit_for_bit(m, n, k, seed):
+    """oracle.dequant_a / dequant_b against the reference's dqa_kernel / dqb_kernel run on the
+    reference's own [k][m] / [k][n] / [k/128][m] / [k/128][ceil(n/128)] storage."""
+    a, b, a_s, b_s, _ = make_inputs(m, n, k, seed)
+    a_km = ref_oracle.dequant_a_km(a, a_s)
+    b_kn = ref_oracle.dequant_b_kn(b, b_s)
+    assert torch.equal(oracle.dequant_a(a, a_s).view(torch.int32), a_km.T.contiguous().view(torch.int32))
+    assert torch.equal(oracle.dequant_b(b, b_s).view(torch.int32), b_kn.T.contiguous().view(torch.int32))
+    # the whole path: the same dequantised bits go into an fp32 matmul on both sides, so the only
+    # difference left is the order in which the BLAS adds K products
+    got = oracle.dequant_matmul_fp32(a, b, a_s, b_s)
+    want = ref_oracle.dequant_matmul_fp32(a, b, a_s, b_s)
+    assert (got - want).abs().max() <= 2e-5 * want.abs().max()
+    ok, excess, max_err = oracle.check(got.to(torch.bfloat16), want.to(torch.bfloat16))
+    assert ok, (excess, max_err)
+
+
+@needs_ref
+def test_reference_kernels_see_every_code():
+    """All 256 byte values through the reference's dqa_kernel with scale 1 give the decode table."""
+    a = torch.arange(256, dtype=torch.uint8).repeat(128, 1).T.contiguous().view(torch.float8_e4m3fn)  # [256, 128]
+    a_s = torch.ones(256, 1)
+    got = ref_oracle.dequant_a_km(a, a_s)[0].numpy()  # k = 0: one value per row = per code
+    want = np.load(os.path.join(GOLDEN, "e4m3fn_table.npy"))
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.array_equal(got[~np.isnan(want)].view(np.uint32), want[~np.isnan(want)].view(np.uint32))
+
+
+@pytest.mark.parametrize("path", CASES, ids=[os.path.basename(p)[:-4] for p in CASES])
+def test_dequantise_matches_the_reference_digests_in_the_fixture(path):
+    """Runs without the reference: the fixtures carry SHA-256 digests of what the reference's kernels
+    produced (in its [k][m] / [k][n] storage); the oracle's dequantised operands must hash the same."""
+    z = np.load(path)
+    a, b, a_s, b_s, c32, c16, (m, n, k, seed, phase) = load_case(path)
+    assert sha(oracle.dequant_a(a, a_s).T) == bytes(z["dq_a_km_sha256"])
+    assert sha(oracle.dequant_b(b, b_s, phase).T) == bytes(z["dq_b_kn_sha256"])
 
 
 @pytest.mark.parametrize("path", CASES, ids=[os.path.basename(p)[:-4] for p in CASES])
