@@ -495,12 +495,22 @@ struct TileCfg {
   // Register split after setmaxnreg (light: producer / MMA / loader warps, heavy: promotion warps):
   // 128 * light + kEpiThreads * heavy is at most the allocation the CTA is launched with
   // (384 threads x 168 registers).
-  static constexpr int kRegsLight = 104;
-  static constexpr int kRegsHeavy = 200;
+#ifndef FP8MM_X_REGS_LIGHT
+#define FP8MM_X_REGS_LIGHT 104
+#define FP8MM_X_REGS_HEAVY 200
+#endif
+#ifndef FP8MM_X_CC256
+#define FP8MM_X_CC256 32
+#endif
+#ifndef FP8MM_X_PACKED256
+#define FP8MM_X_PACKED256 64
+#endif
+  static constexpr int kRegsLight = BN == 256 ? FP8MM_X_REGS_LIGHT : 104;
+  static constexpr int kRegsHeavy = BN == 256 ? FP8MM_X_REGS_HEAVY : 200;
   // Columns fetched from TMEM per tcgen05.ld: as wide as the registers allow without spilling
   // next to the accumulators. tcgen05.wait::ld waits for every outstanding fetch; keeping two
   // 32-column fetches in flight with two landing areas was measured 5-8 % slower than one at a time.
-  static constexpr int kChunkCols = (kColsPerThread == 64) ? 64 : 32;
+  static constexpr int kChunkCols = (kColsPerThread == 64) ? 64 : (BN == 256 ? FP8MM_X_CC256 : 32);
   static constexpr int kChunks = kColsPerThread / kChunkCols;
   // Accumulators as packed pairs (fma.rn.f32x2: half the issue slots) or as scalars. With 128 columns per
   // thread the packed form spills (the pairs want aligned 64-bit registers next to a 32-register landing
@@ -508,11 +518,20 @@ struct TileCfg {
   static constexpr bool kScalarAcc = (BN == 256);
   // At BN=256 the first 64 of a thread's 128 columns stay packed (no spill, 1 % faster than all scalar);
   // 96 packed columns spill again.
-  static constexpr int kPackedCols = kScalarAcc ? 64 : kColsPerThread;
+  static constexpr int kPackedCols = kScalarAcc ? FP8MM_X_PACKED256 : kColsPerThread;
   // Narrow tiles: the promotion warps probe the next K block's barrier (non-blocking) right after they
   // release a buffer, so the answer arrives during the fmas and the blocking wait is skipped when the
   // block is already there. Measured -3 % at 64 and 128 columns, 0 at 256, +2.6 % on 192-wide pairs.
   static constexpr bool kEarlyProbe = (BN <= 128);
+#ifndef FP8MM_X_HALF
+#define FP8MM_X_HALF 0
+#endif
+  // 256-wide pair tiles: a K block is issued as two groups of N=128 instructions (columns 0-127, then
+  // 128-255), each with its own commit, and each promotion warpgroup waits for, drains and hands back
+  // only its own half of the TMEM buffer: four half buffers cycling independently instead of two whole
+  // ones. For that each CTA's share of the B tile is rows {0-63, 128-191} + 64 * rank of the tile (two
+  // TMA boxes), so that an N=128 instruction reading 64 rows from each CTA covers 128 adjacent columns.
+  static constexpr bool kHalf = PAIR && BN == 256 && (FP8MM_X_HALF != 0);
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "block_n must be 64, 128, 192 or 256");
 };
 
@@ -589,11 +608,13 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   uint8_t* ring = smem + kHeaderBytes;
   uint64_t* full_bar = bars;                                 // [kMaxStages]
   uint64_t* done_bar = bars + kMaxStages;                    // [kMaxStages]
+  uint64_t* done_lo_bar = bars + 2 * kMaxStages;             // [kMaxStages], kHalf: commit of columns 0-127
   uint64_t* scale_full_bar = bars + 2 * kMaxStages + 8;      // [kScaleSlots]
   uint64_t* scale_empty_bar = scale_full_bar + kScaleSlots;  // [kScaleSlots]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(scale_empty_bar + kScaleSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
+  uint64_t* hi_free_bar = bars + 40;                         // [kMaxStages], kHalf: columns 128-255 drained
   // staging for the TMA store of c: [warpgroup][buffer][128 rows x 64 B], behind the ring (1024-byte aligned:
   // the header and every stage are multiples of 1024 bytes)
   uint8_t* staging = ring + stages * Cfg::kStageBytes;
@@ -606,8 +627,12 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
       // one arrive.expect_tx per producing CTA + one release per promotion warp (of both CTAs)
-      mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1) * (1 + Cfg::kEpiWarps));
+      mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1) * (1 + (Cfg::kHalf ? Cfg::kEpiWarps / 2 : Cfg::kEpiWarps)));
       mbar_init(smem_u32(&done_bar[s]), 1);  // the MMA thread's commit
+      if constexpr (Cfg::kHalf) {
+        mbar_init(smem_u32(&done_lo_bar[s]), 1);
+        mbar_init(smem_u32(&hi_free_bar[s]), 2 * (Cfg::kEpiWarps / 2));
+      }
     }
     for (int s = 0; s < kScaleSlots; ++s) {
       mbar_init(smem_u32(&scale_full_bar[s]), 32);
@@ -664,7 +689,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
           if (it.skip) continue;
           const int a_row = it.m0 + static_cast<int>(cta_rank) * kBlockM;
-          const int b_row = it.n0 + static_cast<int>(cta_rank) * (PAIR ? Cfg::kRowsB : 0);
+          const int b_row = it.n0 + static_cast<int>(cta_rank) * (PAIR ? (Cfg::kHalf ? 64 : Cfg::kRowsB) : 0);
           for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
             if (!mbar_wait(smem_u32(&done_bar[stage]), phase ^ 1u, ctx, 0x100 | stage)) {
               ok = false;
@@ -677,14 +702,22 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             // K-major: x = byte of K, y = matrix row. MN-major: x = matrix row (a multiple of 64), y = k.
             if (GENERIC && p.groups > 0) {
               tma_load_3d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, it.group, fb);
-              tma_load_3d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
+              if constexpr (Cfg::kHalf) {
+                tma_load_3d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
+                tma_load_3d<PAIR>(sa + Cfg::kStageBytesA + 64 * kBlockK, &tmap_b, kb * kBlockK, b_row + 128, it.group, fb);
+              } else {
+                tma_load_3d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
+              }
             } else {
             if (!GENERIC || !p.a_mn) {
               tma_load_2d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, fb);
             } else {
               tma_load_2d<PAIR>(sa, &tmap_a, a_row, kb * kBlockK, fb);
             }
-            if (!GENERIC || !p.b_mn) {
+            if constexpr (Cfg::kHalf) {
+              tma_load_2d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, fb);
+              tma_load_2d<PAIR>(sa + Cfg::kStageBytesA + 64 * kBlockK, &tmap_b, kb * kBlockK, b_row + 128, fb);
+            } else if (!GENERIC || !p.b_mn) {
               tma_load_2d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, fb);
             } else {
               for (int i = 0; i < p.b_boxes; ++i)
@@ -708,7 +741,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       // thread roughly 100 clocks), more than the tensor pipe needs for a narrow tile's block.
       if (lane == 0 && cta_rank == 0 && warp - 1 < p.issuers) {
         constexpr uint32_t kHiK = (1024u >> 4) | (1u << 14) | (2u << 29);  // K-major, 128-byte swizzle
-        const uint32_t idesc = make_idesc(Cfg::kTileM, BN) | (GENERIC ? p.idesc_major : 0u);
+        const uint32_t idesc = make_idesc(Cfg::kTileM, Cfg::kHalf ? BN / 2 : BN) | (GENERIC ? p.idesc_major : 0u);
         const uint32_t a_hi = GENERIC ? p.a_desc_hi : kHiK, b_hi = GENERIC ? p.b_desc_hi : kHiK;
         const uint32_t a_kstep = GENERIC ? p.a_kstep : 2u, b_kstep = GENERIC ? p.b_kstep : 2u;
         const uint32_t a_lo_bits = GENERIC ? p.a_desc_lo : (1u << 16), b_lo_bits = GENERIC ? p.b_desc_lo : (1u << 16);
@@ -742,6 +775,20 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             for (int k = 0; k < kMmasPerBlock; ++k) {
               // next K=32 slice: 32 bytes further inside the swizzle row (K-major) or 32 rows further
               umma_f8<PAIR>(d_addr, a_lo + a_kstep * k, b_lo + b_kstep * k, a_hi, b_hi, idesc, k > 0 ? 1u : 0u);
+            }
+            if constexpr (Cfg::kHalf) {
+              umma_commit<PAIR>(smem_u32(&done_lo_bar[my_stage]));
+              // columns 128-255: the same A, the second 64 rows of each CTA's share of B
+              if (!mbar_wait(smem_u32(&hi_free_bar[my_stage]), my_phase, ctx, 0x700 | my_stage)) {
+                ok = false;
+                break;
+              }
+              tcgen05_fence_after();
+#pragma unroll
+              for (int k = 0; k < kMmasPerBlock; ++k) {
+                umma_f8<PAIR>(d_addr + BN / 2, a_lo + a_kstep * k, b_lo + ((64u * kBlockK) >> 4) + b_kstep * k, a_hi, b_hi,
+                              idesc, k > 0 ? 1u : 0u);
+              }
             }
             umma_commit<PAIR>(smem_u32(&done_bar[my_stage]));
             my_stage += step;
@@ -821,7 +868,10 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     // "Buffer drained" is reported to the full barrier of the stage whose K block will overwrite the
     // buffer: kTmemBufs K blocks after the one just read. The MMA thread that waits on it lives in
     // the leader CTA.
-    const uint32_t full_base = PAIR ? map_to_cta(smem_u32(&full_bar[0]), 0) : smem_u32(&full_bar[0]);
+    // kHalf: the warpgroup of columns 128-255 reports to the issuer's second barrier of the stage
+    const uint32_t rel_local = (Cfg::kHalf && half == 1) ? smem_u32(&hi_free_bar[0]) : smem_u32(&full_bar[0]);
+    const uint32_t full_base = PAIR ? map_to_cta(rel_local, 0) : rel_local;
+    const uint32_t ready_base = (Cfg::kHalf && half == 0) ? smem_u32(&done_lo_bar[0]) : smem_u32(&done_bar[0]);
     auto release_to = [&](int st) {
       if (lane == 0) {
         if constexpr (PAIR) {
@@ -882,7 +932,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         for (int u = 0; u < kScaleGroup; ++u) {
           if (kb0 + u >= it.kb_end) break;
           if (!(Cfg::kEarlyProbe && ready_next)) {
-            if (!mbar_wait(smem_u32(&done_bar[cstage]), cphase, ctx, 0x400 | cstage)) {
+            if (!mbar_wait(ready_base + static_cast<uint32_t>(cstage * 8), cphase, ctx, 0x400 | cstage)) {
               ok = false;
               break;
             }
@@ -908,31 +958,23 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                   ns = 0;
                   np ^= 1u;
                 }
-                ready_next = mbar_test(smem_u32(&done_bar[ns]), np);
+                ready_next = mbar_test(ready_base + static_cast<uint32_t>(ns * 8), np);
               }
             }
-            const float s = (((gcol0 + ch * CC) >> 7) == jb0) ? s_lo[u] : s_hi[u];
-            const unsigned long long s2 = pack2(s, s);
-            if constexpr (Cfg::kScalarAcc) {
-              if (ch * CC < kPackedCols) {
+            // 32 columns at a time: a scale-row boundary can fall on any multiple of 32 columns
 #pragma unroll
-                for (int j = 0; j < CC / 2; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], s2);
+            for (int q = 0; q < CC / 32; ++q) {
+              const int cb = ch * CC + 32 * q;  // offset inside this thread's columns
+              const float s = (((gcol0 + cb) >> 7) == jb0) ? s_lo[u] : s_hi[u];
+              if (cb < kPackedCols) {
+                const unsigned long long s2 = pack2(s, s);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) fma2(acc2[cb / 2 + j], v[32 * q + 2 * j], v[32 * q + 2 * j + 1], s2);
               } else {
 #pragma unroll
-                for (int j = 0; j < CC; ++j)
-                  accf[ch * CC - kPackedCols + j] = fmaf(__uint_as_float(v[j]), s, accf[ch * CC - kPackedCols + j]);
+                for (int j = 0; j < 32; ++j)
+                  accf[cb - kPackedCols + j] = fmaf(__uint_as_float(v[32 * q + j]), s, accf[cb - kPackedCols + j]);
               }
-            } else if constexpr (CC <= 32) {
-#pragma unroll
-              for (int j = 0; j < CC / 2; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], s2);
-            } else {
-              // a 64-column fetch can straddle a scale-row boundary at its middle
-              const float sb = (((gcol0 + ch * CC + 32) >> 7) == jb0) ? s_lo[u] : s_hi[u];
-              const unsigned long long sb2 = pack2(sb, sb);
-#pragma unroll
-              for (int j = 0; j < 16; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], s2);
-#pragma unroll
-              for (int j = 16; j < 32; ++j) fma2(acc2[ch * (CC / 2) + j], v[2 * j], v[2 * j + 1], sb2);
             }
             if (ch + 1 < Cfg::kChunks) tmem_ld(taddr + static_cast<uint32_t>((ch + 1) * CC), v);
           }
@@ -1188,6 +1230,13 @@ bool encode_output_map_3d(CUtensorMap* map, void* base, int groups, int M, int N
 }
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Rows of b per TMA box of one CTA (K-major b). A pair's 256-wide tile takes its share of b as two boxes of
+// 64 rows (see TileCfg::kHalf).
+int b_box_rows_for(int block_n, int pair) {
+  if (!pair) return block_n;
+  return (block_n == 256 && FP8MM_X_HALF != 0) ? 64 : block_n / 2;
+}
 
 int epi_warps_for(int block_n) {
   (void)block_n;
@@ -1485,7 +1534,7 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
     memset(&map_c, 0, sizeof(map_c));
   }
   const OperandLayout la = operand_layout(a_mn, kBlockM);
-  const OperandLayout lb = operand_layout(b_mn, pl.cta_pair ? pl.block_n / 2 : pl.block_n);
+  const OperandLayout lb = operand_layout(b_mn, b_box_rows_for(pl.block_n, pl.cta_pair));
   if (!encode_operand_map(&map_a, a, M, K, lda, la.box_cols, a_mn)) return B200_FP8_MM_ERR_DRIVER;
   if (!encode_operand_map(&map_b, b, N, K, ldb, lb.box_cols, b_mn)) return B200_FP8_MM_ERR_DRIVER;
 
@@ -1643,7 +1692,7 @@ int run_grouped(const void* a, const void* b, const float* a_scale, const float*
     memset(&map_c, 0, sizeof(map_c));
   }
   if (!encode_operand_map_3d(&map_a, a, groups, M, K, lda, a_g, kBlockM)) return B200_FP8_MM_ERR_DRIVER;
-  const int b_rows_per_cta = pl.cta_pair ? pl.block_n / 2 : pl.block_n;
+  const int b_rows_per_cta = b_box_rows_for(pl.block_n, pl.cta_pair);
   if (!encode_operand_map_3d(&map_b, b, groups, N, K, ldb, b_g, b_rows_per_cta)) return B200_FP8_MM_ERR_DRIVER;
 
   const OperandLayout la = operand_layout(false, kBlockM);

@@ -72,21 +72,30 @@ def workspace_bytes(m: int, n: int, k: int, plan: Plan | None = None) -> int:
     return int(lib.b200_fp8_mm_plan_workspace_bytes(m, n, k, ctypes.byref(cp)))
 
 
-# Per-device scratch owned by the Python side: the library itself allocates nothing. The
-# reference allocates its split-K scratch on every call
-# (1-amd-fp8-mm/amd-fp8-mm-submission.py:600); here it is cached and only ever grows.
-_workspaces: dict[int, torch.Tensor] = {}
+# Scratch owned by the Python side (the library allocates nothing). The reference allocates its split-K
+# scratch on every call (1-amd-fp8-mm/amd-fp8-mm-submission.py:600); here it is cached, one buffer per
+# (device, stream): split-K launches count arrivals in the buffer's first 4096 bytes and park fp32 partials
+# behind them, so two launches that may overlap on the GPU (different streams) must not share one. Launches
+# on one stream run in order and can. A buffer that has to grow is replaced, and the old one is kept alive
+# for the life of the process: a launch queued earlier may still be using it, and handing its memory back
+# to the caching allocator would let another stream's allocation overwrite it.
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_retired_workspaces: list[torch.Tensor] = []
 _status: dict[int, torch.Tensor] = {}
 
 
-def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
+def _workspace(device: torch.device, nbytes: int, stream: int) -> torch.Tensor | None:
     if nbytes == 0:
         return None
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    ws = _workspaces.get(idx)
+    key = (idx, stream)
+    ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired_workspaces.append(ws)
+        # zeroed on the stream that will use it (the current one): the counters must start at zero
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[idx] = ws
+        _workspaces[key] = ws
     return ws
 
 
@@ -169,12 +178,12 @@ def fp8_mm(a, b, a_scale, b_scale, c, n_phase: int = 0, plan: Plan | None = None
     m, k = a.shape
     n = b.shape[0]
     dev = a.device
-    ws = _workspace(dev, nbytes)
-    st = _status_words(dev)
     if dev.index != torch.cuda.current_device():
         with torch.cuda.device(dev):
             return fp8_mm(a, b, a_scale, b_scale, c, n_phase, plan, check)
     stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, nbytes, stream)
+    st = _status_words(dev)
     args = (
         a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), c.data_ptr(),
         m, n, k,
@@ -251,21 +260,98 @@ def check_device_status(device=None):
     words = st.tolist()
     if words[0] != 0:
         st.zero_()
-        ws = _workspaces.get(dev.index if dev.index is not None else torch.cuda.current_device())
-        if ws is not None:
-            ws[:4096].zero_()  # split-K counters may be mid-count after an aborted launch
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        for (d, _stream), ws in _workspaces.items():
+            if d == idx:
+                ws[:4096].zero_()  # split-K counters may be mid-count after an aborted launch
         raise Fp8MmDeviceError(
             f"kernel wait expired: code={words[0]} where=0x{words[1]:x} block={words[2]} parity={words[3]}")
 
 
-def fp8_mm_host(a, b, a_scale, b_scale, c, device="cuda", n_phase: int = 0):
-    """The same operator for HOST tensors: copies the four inputs to `device`, runs the GEMM,
-    copies c back into the caller's host tensor and returns it. This is the call the end-to-end
-    benchmark times (host<->device copies inside)."""
+class _HostPipeline:
+    """Per-device state of `fp8_mm_host`: three streams (copies in, GEMMs, copies out) and the device
+    buffers of the last problem shape, kept between calls so that a call allocates nothing."""
+
+    def __init__(self, dev: torch.device):
+        self.dev = dev
+        self.s_in = torch.cuda.Stream(dev)
+        self.s_mm = torch.cuda.Stream(dev)
+        self.s_out = torch.cuda.Stream(dev)
+        self.key = None
+        self.bufs = None
+
+    def buffers(self, m, n, k, nb):
+        key = (m, n, k, nb)
+        if self.key != key:
+            dev = self.dev
+            self.bufs = (
+                torch.empty(m, k, dtype=torch.float8_e4m3fn, device=dev),
+                torch.empty(n, k, dtype=torch.float8_e4m3fn, device=dev),
+                torch.empty(m, k // SCALE_BLOCK, dtype=torch.float32, device=dev),
+                torch.empty(nb, k // SCALE_BLOCK, dtype=torch.float32, device=dev),
+                torch.empty(m, n, dtype=torch.bfloat16, device=dev),
+            )
+            self.key = key
+        return self.bufs
+
+
+_host_pipelines: dict[int, _HostPipeline] = {}
+
+
+def host_row_chunks(m: int, chunk_rows: int = 512) -> list[tuple[int, int]]:
+    """Row ranges [r0, r1) the host entry point cuts a problem into: a short first range, so that the
+    first copy of c back to the host can start as early as possible, then `chunk_rows` rows each
+    (multiples of 128, the kernel's row block)."""
+    if m <= 256:
+        return [(0, m)]
+    out = [(0, 128)]
+    r = 128
+    while r < m:
+        out.append((r, min(m, r + chunk_rows)))
+        r += chunk_rows
+    return out
+
+
+def fp8_mm_host(a, b, a_scale, b_scale, c, device="cuda", n_phase: int = 0, chunk_rows: int = 512):
+    """The same operator for HOST tensors (pinned memory for full speed): returns c, filled, when done.
+
+    b and b_scale are copied to `device` first; a, a_scale are then streamed in row ranges, each range's
+    GEMM runs as soon as its rows have landed, and its rows of c are copied back while later ranges are
+    still arriving, so both directions of the host link and the SMs work at the same time (three
+    streams, events between them). Every range is an independent GEMM over whole rows, so the result is
+    bit-identical to one GEMM over the whole problem. Device buffers are kept per device between calls
+    of the same shape. This is the call the end-to-end benchmark times."""
     dev = torch.device(device)
-    da, db, das, dbs = (t.to(dev, non_blocking=True) for t in (a, b, a_scale, b_scale))
-    dc = torch.empty(c.shape, dtype=torch.bfloat16, device=dev)
-    fp8_mm(da, db, das, dbs, dc, n_phase=n_phase)
-    c.copy_(dc, non_blocking=True)
-    torch.cuda.current_stream(dev).synchronize()
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    for name, t in (("a", a), ("b", b), ("a_scale", a_scale), ("b_scale", b_scale), ("c", c)):
+        _check(not t.is_cuda, f"{name} must be a host tensor")
+    _check(a.is_contiguous() and b.is_contiguous() and a_scale.is_contiguous() and b_scale.is_contiguous()
+           and c.is_contiguous(), "host tensors must be contiguous")
+    m, k = a.shape
+    n = b.shape[0]
+    pipe = _host_pipelines.get(dev.index)
+    if pipe is None:
+        pipe = _host_pipelines[dev.index] = _HostPipeline(dev)
+    da, db, das, dbs, dc = pipe.buffers(m, n, k, b_scale.shape[0])
+    caller = torch.cuda.current_stream(dev)
+    pipe.s_in.wait_stream(caller)
+    pipe.s_mm.wait_stream(caller)
+    pipe.s_out.wait_stream(caller)
+    with torch.cuda.device(dev):
+        with torch.cuda.stream(pipe.s_in):
+            db.copy_(b, non_blocking=True)
+            dbs.copy_(b_scale, non_blocking=True)
+        for (r0, r1) in host_row_chunks(m, chunk_rows):
+            with torch.cuda.stream(pipe.s_in):
+                da[r0:r1].copy_(a[r0:r1], non_blocking=True)
+                das[r0:r1].copy_(a_scale[r0:r1], non_blocking=True)
+            pipe.s_mm.wait_stream(pipe.s_in)
+            with torch.cuda.stream(pipe.s_mm):
+                fp8_mm(da[r0:r1], db, das[r0:r1], dbs, dc[r0:r1], n_phase=n_phase)
+            pipe.s_out.wait_stream(pipe.s_mm)
+            with torch.cuda.stream(pipe.s_out):
+                c[r0:r1].copy_(dc[r0:r1], non_blocking=True)
+    pipe.s_out.synchronize()
+    caller.wait_stream(pipe.s_out)
     return c

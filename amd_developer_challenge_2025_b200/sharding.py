@@ -135,3 +135,47 @@ def grid_inputs(a, b, a_scale, b_scale, spec: GridSpec):
     """The (a, b, a_scale, b_scale) blocks rank `spec.rank` holds. Views."""
     bb, bs = shard_inputs(b, b_scale, spec.cols)
     return a[spec.row_begin : spec.row_end], bb, a_scale[spec.row_begin : spec.row_end], bs
+
+
+# ---------------------------------------------------------------------------------------------
+# Optional all-gather of c
+# ---------------------------------------------------------------------------------------------
+
+
+def gather_c(c_local, spec, m: int, n: int, group=None):
+    """All-gathers the ranks' blocks of c into the whole [m, n] matrix on every rank.
+
+    `spec` is this rank's GridSpec (or a ShardSpec for the one-dimensional column scheme). One
+    collective: `all_gather_into_tensor` of the blocks (padded to the largest block when the cut is
+    uneven), then a local re-interleave, since rank r's block is a rectangle of c, not a run of its
+    rows. Column shards of equal width need no padding and the re-interleave is one permute. Works
+    with any torch.distributed backend (NCCL over NVLink on the GPUs; gloo in the CPU tests)."""
+    import torch
+    import torch.distributed as dist
+
+    if isinstance(spec, ShardSpec):
+        spec = GridSpec(spec.rank, spec.world, 1, spec.world, 0, m, spec)
+    world = spec.world
+    if world == 1:
+        return c_local
+    if tuple(c_local.shape) != (spec.m_local, spec.n_local):
+        raise ValueError("c_local does not have the shape of this rank's block")
+    blocks = [grid_spec(m, n, world, r, spec.grid_m, spec.grid_n) for r in range(world)]
+    m_max = max(b.m_local for b in blocks)
+    n_max = max(b.n_local for b in blocks)
+    uniform = all(b.m_local == m_max and b.n_local == n_max for b in blocks)
+    if uniform:
+        send = c_local.contiguous()
+    else:
+        send = c_local.new_zeros(m_max, n_max)
+        send[: spec.m_local, : spec.n_local] = c_local
+    flat = c_local.new_empty(world * m_max, n_max)  # the blocks end to end along dim 0
+    dist.all_gather_into_tensor(flat, send, group=group)
+    recv = flat.view(world, m_max, n_max)
+    if uniform:
+        # [grid_m, grid_n, m_loc, n_loc] -> [grid_m, m_loc, grid_n, n_loc] -> [m, n]
+        return recv.view(spec.grid_m, spec.grid_n, m_max, n_max).permute(0, 2, 1, 3).reshape(m, n)
+    out = c_local.new_empty(m, n)
+    for r, b in enumerate(blocks):
+        out[b.row_begin : b.row_end, b.cols.col_begin : b.cols.col_end] = recv[r, : b.m_local, : b.n_local]
+    return out

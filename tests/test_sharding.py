@@ -9,7 +9,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from amd_developer_challenge_2025_b200.inputs import make_inputs
-from amd_developer_challenge_2025_b200.sharding import choose_grid, grid_inputs, grid_spec, shard_inputs, shard_spec
+from amd_developer_challenge_2025_b200.sharding import (choose_grid, gather_c, grid_inputs, grid_spec, shard_inputs,
+                                                      shard_spec)
 from oracle import fp8_mm_oracle as oracle
 
 
@@ -101,36 +102,44 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, m, n, k, out):
+def _rank_main(rank, world, port, m, n, k, grid, out):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         torch.set_num_threads(1)
         a, b, a_s, b_s, _ = make_inputs(m, n, k, seed=77)
-        spec = shard_spec(n, world, rank)
-        bb, bs = shard_inputs(b, b_s, spec)
-        mine = oracle.dequant_matmul(a, bb.contiguous(), a_s, bs.contiguous(), spec.n_phase)
-        # all_gather concatenates along dim 0: gather [world][M][N/world] and re-interleave
-        gathered = torch.empty(world * m, spec.n_local, dtype=torch.bfloat16)
-        dist.all_gather_into_tensor(gathered, mine.contiguous())
-        c = gathered.view(world, m, spec.n_local).permute(1, 0, 2).reshape(m, n)
+        if grid is None:
+            spec = shard_spec(n, world, rank)   # the one-dimensional column scheme
+            bb, bs = shard_inputs(b, b_s, spec)
+            mine = oracle.dequant_matmul(a, bb.contiguous(), a_s, bs.contiguous(), spec.n_phase)
+        else:
+            spec = grid_spec(m, n, world, rank, *grid)
+            aa, bb, aas, bs = grid_inputs(a, b, a_s, b_s, spec)
+            mine = oracle.dequant_matmul(aa, bb, aas, bs, spec.n_phase)
+        c = gather_c(mine, spec, m, n)
         full = oracle.dequant_matmul(a, b, a_s, b_s)
-        if rank == 0:
-            out.put(bool(torch.equal(c.view(torch.int16), full.view(torch.int16))))
+        out.put((rank, bool(torch.equal(c.view(torch.int16), full.view(torch.int16)))))
         dist.barrier()
     finally:
         dist.destroy_process_group()
 
 
-def test_two_gloo_ranks_gather_equals_unsharded():
+# (world, m, n, k, grid): column shards of equal width; a 2 x 1 row cut; a 2 x 2 grid whose row blocks are
+# uneven (5 row units over 2) and whose column blocks are uneven too (9 column units over 2)
+@pytest.mark.parametrize("world,m,n,k,grid", [(2, 8, 1152, 256, None), (2, 256, 256, 128, (2, 1)),
+                                              (4, 520, 576, 128, (2, 2))])
+def test_gloo_ranks_gather_equals_unsharded(world, m, n, k, grid):
+    """The oracle stands in for the kernel on each rank; what is tested is the shard arithmetic and
+    gather_c's collective + re-interleave, on every rank."""
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, 8, 1152, 256, out)) for r in range(2)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, m, n, k, grid, out)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
-        p.join(120)
+        p.join(180)
         assert p.exitcode == 0
-    assert out.get(timeout=5) is True
+    got = sorted(out.get(timeout=5) for _ in range(world))
+    assert got == [(r, True) for r in range(world)]
