@@ -21,7 +21,7 @@ from __future__ import annotations
 
 import argparse
 import json
-import re
+import os
 import statistics
 import sys
 
@@ -31,16 +31,16 @@ from .fp8_mm import check_device_status, describe
 from .inputs import make_inputs
 from .submission import custom_kernel
 
-# The competition's benchmark grid as the reference describes it (README.md:62-82): two values of m
-# times nine (n, k) pairs. The harness's own seeds belong to its task files and are not reproduced;
-# seeds here are derived from the shape.
-COMPETITION_M = (1024, 6144)
-COMPETITION_NK = ((1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
-                  (512, 7168), (4096, 512))
+# The competition's benchmark cases as the reference lists them (README.md:65-82): two values of m times
+# nine (n, k) pairs, each with its seed. competition_spec.txt holds those lines, copied from the reference's
+# README by make_competition_spec.py.
+COMPETITION_SPEC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "competition_spec.txt")
 
 
 def competition_cases():
-    return [(m, n, k, (m * 31 + n * 17 + k) % 100003) for m in COMPETITION_M for (n, k) in COMPETITION_NK]
+    """[(m, n, k, seed)] of the 18 cases, in the reference's order."""
+    with open(COMPETITION_SPEC, "r", encoding="utf-8") as f:
+        return parse_spec(f.read())
 
 
 RTOL, ATOL = 2e-2, 1e-3
@@ -114,7 +114,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("mode", choices=("test", "benchmark"))
     ap.add_argument("spec", nargs="?", help="spec file; omit with --competition-shapes")
-    ap.add_argument("--competition-shapes", action="store_true", help="the 2 x 9 shape grid the reference describes")
+    ap.add_argument("--competition-shapes", action="store_true", help="the 18 cases (shape and seed) the reference lists")
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--layout", choices=("k", "mn"), default="k",
                     help="storage of a and b: K contiguous, or the harness's [K][M] / [K][N] (mn)")

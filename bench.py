@@ -3,13 +3,18 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-sweep]
 
 One "step" is one GEMM of the headline workload M=8192, N=4608, K=7168 (e4m3fn a/b, fp32 block
-scales, bf16 out). With N GPUs the columns of b/b_scale are sharded over the ranks (strong
-scaling: the total problem is fixed), a/a_scale are replicated and c stays sharded; there is no
-data-path collective. Rank 0 prints ONE JSON line.
+scales, bf16 out). With N GPUs (one process per GPU under torch.distributed.run) the total problem is
+fixed (strong scaling) and c stays sharded; there is no data-path collective. Two partitions are timed
+in the same run:
 
---impl reference times the reference's own algorithm for this path on the host cores (the CPU
-restatement of its dequantise-then-matmul script; the reference's HIP sources cannot be built
-for a CUDA machine) on a bounded row sample of the same workload.
+* `value`: the configuration's stated one, b / b_scale cut along N only (576 columns per GPU at 8; odd
+  ranks start 64 columns into a scale block), a / a_scale replicated;
+* `row_column_grid`: the grid of row x column blocks the library's cost model rates fastest
+  (4 x 2 at 8 GPUs), reported beside it.
+
+Rank 0 prints ONE JSON line. `--impl reference` times the reference's own path for this operator on
+the host cores: its two dequantise kernels (compiled for the host from the reference's text when that
+was possible, else the CPU restatement) followed by the fp32 matmul, on the full problem.
 """
 from __future__ import annotations
 
@@ -17,7 +22,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -34,9 +38,11 @@ UNIT = "TFLOP/s"
 NOMINAL_FP8_TFLOPS = 4500.0
 FALLBACK_BF16_TFLOPS = 1590.0
 L2_BYTES = 126 * 1024 * 1024
-# DRAM bytes of one launch of the headline GEMM on one GPU, from an ncu capture of that launch
-# (dram__bytes_read.sum 113.7 MB + dram__bytes_write.sum 57.4 MB).
-HEADLINE_DRAM_BYTES = 171_100_000
+# DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of that launch
+# with operands that were not in L2); the summaries under profiles/ give the commands.
+MEASURED_DRAM_BYTES = {
+    (8192, 4608, 7168): 171_100_000,
+}
 SWEEP_NK = ((1536, 7168), (3072, 1536), (576, 7168), (7168, 256), (7168, 2048), (4608, 7168), (7168, 2304),
             (512, 7168), (4096, 512))
 SWEEP_M = (512, 2048, 8192, 16384)
@@ -59,58 +65,72 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while a region is timed."""
+    """Reads (never sets) the SM clock, power draw and clock-event reasons of one GPU through NVML every
+    10 ms on a thread of its own, each sample stamped with time.monotonic(), so that the samples that
+    fall inside a timed region can be picked out afterwards."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", "nvmlClocksEventReasonHwSlowdown"),
+               ("hw_thermal_slowdown", "nvmlClocksEventReasonHwThermalSlowdown"),
+               ("sw_thermal_slowdown", "nvmlClocksEventReasonSwThermalSlowdown"),
+               ("sw_power_cap", "nvmlClocksEventReasonSwPowerCap"))
 
-    def __init__(self, index: int):
-        self.index = index
-        self.rows = []
-        self.proc = None
+    def __init__(self, cuda_index: int):
+        self.rows = []  # (t, sm_mhz, power_w, reason bits)
+        self.stop_flag = threading.Event()
         self.thread = None
+        self.handle = None
+        self.max_mhz = None
+        self.error = None
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(cuda_index).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(cuda_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # no NVML: report that instead of numbers
+            self.error = f"{type(e).__name__}: {e}"
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        if self.handle is None:
             return
-        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) >= 7:
-                self.rows.append(parts)
+    def _loop(self):
+        nv = self.nv
+        while not self.stop_flag.is_set():
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                watts = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                bits = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                self.rows.append((time.monotonic(), mhz, watts, bits))
+            except Exception as e:
+                self.error = f"{type(e).__name__}: {e}"
+                return
+            time.sleep(0.01)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, r[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        # the first samples precede the warm-up: drop the leading quarter
-        sm_load = sm[len(sm) // 4:] if len(sm) >= 4 else sm
-        return {"sm_mhz": statistics.median(sm_load) if sm_load else None,
-                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm), "reasons": sorted(reasons)}
+        self.stop_flag.set()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+
+    def summary(self, t0: float, t1: float, window: str):
+        if self.handle is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [f"NVML unavailable ({self.error})"]}
+        rows = [r for r in self.rows if t0 <= r[0] <= t1]
+        reasons = set()
+        for name, attr in self.REASONS:
+            bit = int(getattr(self.nv, attr))
+            if any(r[3] & bit for r in rows):
+                reasons.add(name)
+        return {"sm_mhz": statistics.median(r[1] for r in rows) if rows else None, "sm_max_mhz": self.max_mhz,
+                "power_w_max": round(max(r[2] for r in rows), 1) if rows else None, "samples": len(rows),
+                "window": window, "reasons": sorted(reasons)}
 
 
 def dist_env():
@@ -145,9 +165,9 @@ def time_launches(fn_list, steps, warmup):
     return e0.elapsed_time(e1) / steps
 
 
-def spot_check(pkg, a, b, a_s, b_s, c, n_phase=0, rows=128):
+def spot_check(a, b, a_s, b_s, c, n_phase=0, rows=128):
     """Cheap on-device check of `rows` rows against an fp32 dequantise-then-matmul in torch
-    (the full CPU-oracle parity runs in tests/); contract tolerance rtol=2e-2, atol=1e-3."""
+    (the CPU-oracle parity of every benchmarked shape runs in tests/); contract tolerance rtol=2e-2, atol=1e-3."""
     m, n = c.shape
     idx = torch.linspace(0, m - 1, min(rows, m), device=c.device).long()
     jb = (torch.arange(n, device=c.device) + n_phase) // 128
@@ -158,31 +178,52 @@ def spot_check(pkg, a, b, a_s, b_s, c, n_phase=0, rows=128):
     return bool(((got - ref).abs() <= 1e-3 + 2e-2 * ref.abs()).all().item())
 
 
-def cpu_oracle_tflops(n, k, target_seconds, threads=None):
-    """Times the CPU restatement of the reference's path on a row sample of the workload."""
-    from oracle import fp8_mm_oracle as oracle
-    from amd_developer_challenge_2025_b200.inputs import make_inputs
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the reference's path on the host cores
+# ---------------------------------------------------------------------------------------------
 
-    if threads:
-        torch.set_num_threads(threads)
-    rows = 64
-    a, b, a_s, b_s, _ = make_inputs(rows, n, k, seed=3)
-    oracle.dequant_matmul(a, b, a_s, b_s)  # warm-up (thread pools, allocator)
-    t0 = time.perf_counter()
-    oracle.dequant_matmul(a, b, a_s, b_s)
-    t_probe = time.perf_counter() - t0
-    # the dequantisation of b is a fixed cost per call; scale rows so one call takes ~target/3 s
-    rows = int(max(64, min(8192, rows * (target_seconds / 3.0) / max(t_probe, 1e-4))))
-    rows = (rows // 64) * 64
-    a, b, a_s, b_s, _ = make_inputs(rows, n, k, seed=4)
-    times = []
-    t_all = time.perf_counter()
-    while len(times) < 3 or (time.perf_counter() - t_all < target_seconds and len(times) < 20):
+
+def host_threads() -> int:
+    """All the host threads this process may use (torch.distributed.run exports OMP_NUM_THREADS=1,
+    which would otherwise pin the CPU arm to one thread)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(1, n)
+
+
+class CpuPath:
+    """The reference's dequantise-then-matmul on the host, timed per call on the full problem.
+    kind "reference": its own dqa/dqb kernels compiled for the host + the script's `a_fp32.T @ b_fp32`;
+    kind "port": the CPU restatement, when the compiled kernels are not available on this machine."""
+
+    def __init__(self, m, n, k, seed=3):
+        from amd_developer_challenge_2025_b200.inputs import make_inputs
+        from oracle import fp8_mm_oracle, ref_oracle
+
+        self.threads = host_threads()
+        torch.set_num_threads(self.threads)
+        os.environ["OMP_NUM_THREADS"] = str(self.threads)
+        self.m, self.n, self.k = m, n, k
+        self.inputs = make_inputs(m, n, k, seed)[:4]
+        if ref_oracle.available():
+            self.kind = "reference"
+            prepared = ref_oracle.Prepared(*self.inputs)  # the reference's [k][m] / [k][n] storage, made once
+            self.fn = prepared.run
+        else:
+            self.kind = "port"
+            self.fn = lambda: fp8_mm_oracle.dequant_matmul(*self.inputs)
+
+    def step(self) -> float:
         t0 = time.perf_counter()
-        oracle.dequant_matmul(a, b, a_s, b_s)
-        times.append(time.perf_counter() - t0)
-    t = statistics.median(times)
-    return 2.0 * rows * n * k / t / 1e12, rows, torch.get_num_threads(), t
+        self.fn()
+        return time.perf_counter() - t0
+
+    def describe(self) -> str:
+        what = ("the reference's dqa/dqb kernels compiled for the host + torch fp32 matmul" if self.kind == "reference"
+                else "torch CPU restatement of the reference's dequantise-then-matmul")
+        return f"full problem M={self.m} N={self.n} K={self.k} per step; {what}; {self.threads} threads"
 
 
 def run_reference(args):
@@ -190,29 +231,163 @@ def run_reference(args):
     if rank != 0:
         return
     m, n, k = HEADLINE
-    per_step = []
-    rows_used = 0
-    threads = 0
-    total = args.warmup + args.steps
-    budget = max(2.0, min(20.0, 120.0 / max(total, 1)))
-    for i in range(total):
-        tf, rows_used, threads, t = cpu_oracle_tflops(n, k, budget)
+    cpu = CpuPath(m, n, k)
+    times = []
+    for i in range(args.warmup + args.steps):
+        t = cpu.step()
         if i >= args.warmup:
-            per_step.append((tf, t))
-    tf = statistics.median(x[0] for x in per_step)
-    sample = f"rows 0..{rows_used - 1} of a (M sample {rows_used} of {m}), full N={n}, K={k}; torch CPU fp32"
+            times.append(t)
+    t_step = statistics.mean(times)
+    tf = 2.0 * m * n * k / t_step / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": round(tf, 4), "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(2.0 * m * n * k / (tf * 1e12) * 1e3, 3), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (e4m3fn inputs dequantised on CPU)",
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(t_step * 1e3, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (e4m3fn inputs dequantised on the CPU)",
         "data": "synthetic",
         "config": {"workload": "fp8_block_scaled_gemm M=8192 N=4608 K=7168", "path": "CPU dequantise-then-matmul"},
-        "cpu_baseline": {"value": round(tf, 4), "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": round(tf, 4), "unit": UNIT, "cores": cpu.threads, "kind": cpu.kind,
+                         "sample": cpu.describe()},
         "e2e": {"value": round(tf, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+
+
+class Ranks:
+    def __init__(self, dev, world):
+        self.dev, self.world, self.dist = dev, world, None
+        if world > 1:
+            import torch.distributed as dist_mod
+
+            self.dist = dist_mod
+            dist_mod.init_process_group("nccl", device_id=dev)
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def _reduce(self, x: float, op) -> float:
+        if self.dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    def max(self, x: float) -> float:
+        return self._reduce(x, self.dist.ReduceOp.MAX if self.dist else None)
+
+    def all_true(self, ok: bool) -> bool:
+        return self._reduce(1.0 if ok else 0.0, self.dist.ReduceOp.MIN if self.dist else None) > 0.5
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+
+
+def partition_sets(pkg, m_full, n, k, spec, dev, seed0=1000):
+    """Rotating input/output sets of one rank's block, more than twice the L2 in total."""
+    m, n_loc = spec.m_local, spec.n_local
+    set_bytes = m * k + n_loc * k + 2 * m * n_loc
+    nsets = max(2, -(-(2 * L2_BYTES + 64 * 1024 * 1024) // set_bytes))
+    sets = []
+    for s in range(nsets):
+        a, b, a_s, b_s = gpu_inputs(m_full, n, k, seed0 + s, dev)
+        aa, bb, aas, bs = pkg.grid_inputs(a, b, a_s, b_s, spec)
+        sets.append((aa.contiguous(), bb.contiguous(), aas.contiguous(), bs.contiguous(),
+                     torch.empty(m, n_loc, dtype=torch.bfloat16, device=dev)))
+        del a, b, a_s, b_s
+    return sets, set_bytes
+
+
+def time_partition(pkg, ranks, m_full, n, k, grid, rank, steps, warmup, dev, sampler=None):
+    """Times `steps` GEMMs of this rank's block of the (grid_m x grid_n) partition: barrier + synchronize
+    on both sides, CUDA events on the launching stream, max over ranks."""
+    from amd_developer_challenge_2025_b200.fp8_mm import check_device_status
+
+    spec = pkg.grid_spec(m_full, n, ranks.world, rank, grid[0], grid[1])
+    sets, set_bytes = partition_sets(pkg, m_full, n, k, spec, dev)
+    fns = [(lambda t=t: pkg.fp8_mm(t[0], t[1], t[2], t[3], t[4], n_phase=spec.n_phase)) for t in sets]
+    fns[0]()
+    check_device_status(dev)
+    ok = ranks.all_true(spot_check(*sets[0], n_phase=spec.n_phase))
+    ranks.barrier()
+    t0 = time.monotonic()
+    ms_local = time_launches(fns, steps, warmup)
+    t1 = time.monotonic()
+    ranks.barrier()
+    ms = ranks.max(ms_local)
+    check_device_status(dev)
+    plan = pkg.describe(spec.m_local, spec.n_local, k, spec.n_phase)
+    out = {"spec": spec, "sets": sets, "set_bytes": set_bytes, "ms": ms, "ms_local": ms_local, "ok": ok, "plan": plan,
+           "window": (t0, t1), "fns": fns}
+    return out
+
+
+def plan_text(plan):
+    return f"{'2x' if plan.cta_pair else ''}128x{plan.block_n} split{plan.split_k} stages{plan.stages} grid{plan.grid}"
+
+
+def sweep_shapes(pkg, ranks, rank, dev, peaks, fp8_peak):
+    """Every shape of the sweep (and the three named configurations): one CUDA graph of one launch per rotating
+    buffer set, device-timed; with several GPUs each rank runs its block of the cost model's grid and the
+    slowest rank counts. The check is MIN over ranks."""
+    from amd_developer_challenge_2025_b200.fp8_mm import check_device_status
+
+    world = ranks.world
+    shapes = list(NAMED_CONFIGS) + [(mm, nn, kk) for mm in SWEEP_M for (nn, kk) in SWEEP_NK]
+    rows = []
+    for (mm, nn, kk) in shapes:
+        try:
+            grid = pkg.choose_grid(mm, nn, kk, world)
+        except ValueError:
+            continue
+        spec = pkg.grid_spec(mm, nn, world, rank, grid[0], grid[1])
+        ml, nl = spec.m_local, spec.n_local
+        set_b = ml * kk + nl * kk + 2 * ml * nl
+        nset = max(2, min(12, -(-(2 * L2_BYTES) // set_b)))
+        ins, outs = [], []
+        for i in range(nset):
+            a, b, a_s, b_s = gpu_inputs(mm, nn, kk, mm + nn + kk + i, dev)
+            ins.append(tuple(t.contiguous() for t in pkg.grid_inputs(a, b, a_s, b_s, spec)))
+            outs.append(torch.empty(ml, nl, dtype=torch.bfloat16, device=dev))
+            del a, b, a_s, b_s
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            # first call on this stream outside the capture: the wrapper's per-stream workspace is made here
+            pkg.fp8_mm(*ins[0], outs[0], n_phase=spec.n_phase)
+            side.synchronize()
+            good = spot_check(*ins[0], outs[0], n_phase=spec.n_phase, rows=64)
+            with torch.cuda.graph(graph, stream=side):
+                for t, o in zip(ins, outs):
+                    pkg.fp8_mm(*t, o, n_phase=spec.n_phase)
+        torch.cuda.synchronize()
+        reps = max(3, 48 // nset)
+        ranks.barrier()
+        t_ms = ranks.max(time_launches([graph.replay], reps, 2) / nset)
+        good = ranks.all_true(good)
+        pl = pkg.describe(ml, nl, kk, spec.n_phase)
+        tf = 2.0 * mm * nn * kk / (t_ms * 1e-3) / 1e12
+        gbs = world * algorithmic_bytes(ml, nl, kk) / (t_ms * 1e-3) / 1e9
+        row = {"m": mm, "n": nn, "k": kk, "us": round(t_ms * 1e3, 2), "tflops": round(tf, 1),
+               "pct_fp8_peak_measured": round(100 * tf / (fp8_peak * world), 1),
+               "pct_fp8_peak_nominal": round(100 * tf / (NOMINAL_FP8_TFLOPS * world), 1),
+               "gbs": round(gbs, 1), "pct_hbm_measured": round(100 * gbs / (peaks["hbm_gbs"] * world), 1),
+               "plan": f"{'2x' if pl.cta_pair else ''}128x{pl.block_n} split{pl.split_k} st{pl.stages}",
+               "pass": good}
+        if world > 1:
+            row["grid"] = f"{grid[0]}x{grid[1]}"
+        if (mm, nn, kk) in MEASURED_DRAM_BYTES and world == 1:
+            row["dram_bytes"] = MEASURED_DRAM_BYTES[(mm, nn, kk)]
+        rows.append(row)
+        del ins, outs, graph
+    check_device_status(dev)
+    return rows
 
 
 def run_ours(args):
@@ -226,59 +401,47 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
+    ranks = Ranks(dev, world)
 
-        dist = dist_mod
-        dist.init_process_group("nccl", device_id=dev)
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(x: float) -> float:
-        if dist is None:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    m, n, k = HEADLINE if not args.shape else tuple(int(x) for x in args.shape.split(","))
-    # The ranks form a grid of row blocks x column blocks of c (no collective either way); the grid is the one
-    # whose slowest rank the library's cost model rates fastest (8 GPUs: 4 x 2, one wave of 256 x 256 pair
-    # tiles per GPU, where 1 x 8 would leave each GPU 2.2 waves of narrower tiles).
-    grid_m, grid_n = (tuple(int(x) for x in args.grid.split("x")) if args.grid else pkg.choose_grid(m, n, k, world))
-    spec = pkg.grid_spec(m, n, world, rank, grid_m, grid_n)
-    m_full, m = m, spec.m_local
-    n_loc = spec.n_local
-    set_bytes = m * k + n_loc * k + 2 * m * n_loc
-    nsets = max(2, -(-(2 * L2_BYTES + 64 * 1024 * 1024) // set_bytes))
-    sets = []
-    for s in range(nsets):
-        a, b, a_s, b_s = gpu_inputs(m_full, n, k, 1000 + s, dev)
-        aa, bb, aas, bs = pkg.grid_inputs(a, b, a_s, b_s, spec)
-        sets.append((aa.contiguous(), bb.contiguous(), aas.contiguous(), bs.contiguous(),
-                     torch.empty(m, n_loc, dtype=torch.bfloat16, device=dev)))
-        del a, b, a_s, b_s
-    plan = pkg.describe(m, n_loc, k, spec.n_phase)
-    fns = [(lambda t=t: pkg.fp8_mm(t[0], t[1], t[2], t[3], t[4], n_phase=spec.n_phase)) for t in sets]
-
-    # correctness of what is about to be timed
-    fns[0]()
-    check_device_status(dev)
-    ok = spot_check(pkg, *sets[0], n_phase=spec.n_phase)
+    m_full, n, k = HEADLINE if not args.shape else tuple(int(x) for x in args.shape.split(","))
+    stated = (1, world)  # the configuration's partition: columns only
+    chosen = tuple(int(x) for x in args.grid.split("x")) if args.grid else pkg.choose_grid(m_full, n, k, world)
 
     sampler = ClockSampler(local) if rank == 0 else None
-    barrier()
     if sampler:
-        sampler.start()
-    ms_local = time_launches(fns, args.steps, args.warmup)
-    barrier()
-    clocks = sampler.stop() if sampler else None  # samples cover the timed GEMM loop only
-    ms = max_over_ranks(ms_local)
-    check_device_status(dev)
+        sampler.start()  # runs from before the warm-up to the end of the sustained loop
+
+    main_run = time_partition(pkg, ranks, m_full, n, k, stated, rank, args.steps, args.warmup, dev)
+    spec, sets, ms, ms_local = main_run["spec"], main_run["sets"], main_run["ms"], main_run["ms_local"]
+    m, n_loc = spec.m_local, spec.n_local
+
+    # A loop long enough for the power cap to settle and for the clock sampler to see it (>= 1 s), beside the
+    # K-step figure above, which at small K lasts a few milliseconds.
+    sus_steps = max(args.steps, int(1000.0 / max(ms_local, 1e-3)) + 1)
+    ranks.barrier()
+    ts0 = time.monotonic()
+    sus_local = time_launches(main_run["fns"], sus_steps, 3)
+    ts1 = time.monotonic()
+    ranks.barrier()
+    sus_ms = ranks.max(sus_local)
+    clocks = None
+    if sampler:
+        sampler.stop()
+        t0, t1 = main_run["window"]
+        clocks = sampler.summary(t0, t1, f"the {args.steps} timed steps (+ warm-up)")
+        if clocks.get("samples", 0) < 3:
+            clocks = sampler.summary(ts0, ts1, f"the sustained loop of {sus_steps} steps that follows the timed steps "
+                                               f"(the timed region is shorter than three 10 ms samples)")
+
+    grid_run = None
+    if world > 1 and chosen != stated:
+        del main_run["fns"]
+        g = time_partition(pkg, ranks, m_full, n, k, chosen, rank, args.steps, args.warmup, dev)
+        grid_run = {"grid": f"{chosen[0]}x{chosen[1]}", "ms_per_step": round(g["ms"], 5),
+                    "value": round(2.0 * m_full * n * k / (g["ms"] * 1e-3) / 1e12, 2), "unit": UNIT,
+                    "block": f"{g['spec'].m_local} rows x {g['spec'].n_local} columns per GPU",
+                    "plan": plan_text(g["plan"]), "spot_check_pass": g["ok"]}
+        del g
 
     # The same GEMM with a and b in the harness's MN-major storage ([K][M], [K][N]), consumed in place.
     mn_ms = None
@@ -311,89 +474,74 @@ def run_ours(args):
         grouped = {"groups": gg, "m": gm, "n": gn, "k": gk, "ms": round(t_one, 5),
                    "tflops": round(gflop / (t_one * 1e-3) / 1e12, 1),
                    "separate_launches_ms": round(t_sep, 5),
-                   "pass": bool(spot_check(pkg, ga[3], gb[3], gas[3], gbs[3], gc[3], rows=64))}
+                   "pass": bool(spot_check(ga[3], gb[3], gas[3], gbs[3], gc[3], rows=64))}
         del ga, gb, gas, gbs, gc
 
-    # Optional all-gather of the column shards of c (not part of the timed GEMM; reported beside it).
-    gather_ms = None
-    if dist is not None and n % grid_n == 0 and m_full % (128 * grid_m) == 0:
-        gathered = torch.empty(world, m, n_loc, dtype=torch.bfloat16, device=dev)
-        for _ in range(3):
-            dist.all_gather_into_tensor(gathered, sets[0][4])
-        barrier()
+    # Optional all-gather of c over NVLink (NCCL), through the package's gather_c; outside the timed GEMM.
+    gather = None
+    if world > 1:
+        a, b, a_s, b_s = gpu_inputs(m_full, n, k, 1000, dev)  # the whole problem of set 0, same bits on every rank
+        whole = pkg.gather_c(sets[0][4], spec, m_full, n)
+        gather_ok = ranks.all_true(spot_check(a, b, a_s, b_s, whole, rows=96))
+        del a, b, a_s, b_s, whole
+        for _ in range(2):
+            pkg.gather_c(sets[0][4], spec, m_full, n)
+        ranks.barrier()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         g0.record()
         for _ in range(10):
-            dist.all_gather_into_tensor(gathered, sets[0][4])
+            pkg.gather_c(sets[0][4], spec, m_full, n)
         g1.record()
         torch.cuda.synchronize()
-        gather_ms = max_over_ranks(g0.elapsed_time(g1) / 10)
-        del gathered
+        gather = {"ms": round(ranks.max(g0.elapsed_time(g1) / 10), 4), "bytes_per_rank": 2 * m * n_loc,
+                  "pass": gather_ok,
+                  "note": "gather_c: NCCL all_gather_into_tensor of the bf16 blocks + re-interleave into [M, N]; "
+                          "checked against the whole problem's inputs on every rank; outside the timed GEMM"}
 
     # end to end through the public call with host buffers (pinned), copies inside the timed region
     ha, hb, has_, hbs = (t.cpu().pin_memory() for t in sets[0][:4])
     hc = torch.empty(m, n_loc, dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(3, min(args.steps, 20))
-    for _ in range(2):
+    for _ in range(3):
         pkg.fp8_mm_host(ha, hb, has_, hbs, hc, device=dev, n_phase=spec.n_phase)
-    barrier()
-    t0 = time.perf_counter()
+    e2e_ok = ranks.all_true(bool(torch.equal(hc.view(torch.int16), sets[0][4].cpu().view(torch.int16))))
+    ranks.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
         pkg.fp8_mm_host(ha, hb, has_, hbs, hc, device=dev, n_phase=spec.n_phase)
     e1.record()
     torch.cuda.synchronize()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
-    _ = time.perf_counter() - t0
-    barrier()
+    e2e_ms = ranks.max(e0.elapsed_time(e1) / e2e_steps)
+    ranks.barrier()
     h2d = sum(t.numel() * t.element_size() for t in (ha, hb, has_, hbs))
     d2h = hc.numel() * hc.element_size()
+    del ha, hb, has_, hbs, hc
 
     flops = 2.0 * m_full * n * k
     value = flops / (ms * 1e-3) / 1e12
     peaks = measured_peaks()
     fp8_peak = 2.0 * peaks["bf16_tflops"]
     per_gpu_tflops = 2.0 * m * n_loc * k / (ms_local * 1e-3) / 1e12
+    nsets, set_bytes = len(sets), main_run["set_bytes"]
+    plan, ok = main_run["plan"], main_run["ok"]
+    del sets, main_run
 
     per_shape = []
+    if not args.no_sweep and not args.shape:
+        per_shape = sweep_shapes(pkg, ranks, rank, dev, peaks, fp8_peak)
+
     cpu_baseline = None
     if rank == 0 and world == 1:
-        if not args.no_sweep and not args.shape:
-            shapes = list(NAMED_CONFIGS) + [(mm, nn, kk) for mm in SWEEP_M for (nn, kk) in SWEEP_NK]
-            for (mm, nn, kk) in shapes:
-                # enough rotating input/output sets that consecutive launches do not find their
-                # operands in L2 (capped at 12 sets), one CUDA graph of one launch per set
-                set_b = mm * kk + nn * kk + 2 * mm * nn
-                nset = max(2, min(12, -(-(2 * L2_BYTES) // set_b)))
-                ins = [gpu_inputs(mm, nn, kk, mm + nn + kk + i, dev) for i in range(nset)]
-                outs = [torch.empty(mm, nn, dtype=torch.bfloat16, device=dev) for _ in range(nset)]
-                pkg.fp8_mm(*ins[0], outs[0])
-                good = spot_check(pkg, *ins[0], outs[0], rows=64)
-                graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
-                with torch.cuda.stream(side):
-                    with torch.cuda.graph(graph, stream=side):
-                        for t, o in zip(ins, outs):
-                            pkg.fp8_mm(*t, o)
-                torch.cuda.synchronize()
-                reps = max(3, 48 // nset)
-                t_ms = time_launches([graph.replay], reps, 2) / nset
-                pl = pkg.describe(mm, nn, kk)
-                tf = 2.0 * mm * nn * kk / (t_ms * 1e-3) / 1e12
-                gbs = algorithmic_bytes(mm, nn, kk) / (t_ms * 1e-3) / 1e9
-                per_shape.append({
-                    "m": mm, "n": nn, "k": kk, "us": round(t_ms * 1e3, 2), "tflops": round(tf, 1),
-                    "pct_fp8_peak_measured": round(100 * tf / fp8_peak, 1),
-                    "pct_fp8_peak_nominal": round(100 * tf / NOMINAL_FP8_TFLOPS, 1),
-                    "gbs": round(gbs, 1), "pct_hbm_measured": round(100 * gbs / peaks["hbm_gbs"], 1),
-                    "plan": f"{'2x' if pl.cta_pair else ''}128x{pl.block_n} split{pl.split_k} st{pl.stages}",
-                    "pass": good})
-                del ins, outs, graph
-            check_device_status(dev)
-        tf_cpu, rows_used, threads, _t = cpu_oracle_tflops(n, k, 12.0)
-        cpu_baseline = {"value": round(tf_cpu, 4), "unit": UNIT, "cores": threads, "kind": "port",
-                        "sample": f"M sample {rows_used} of {m} rows, full N={n}, K={k}; torch CPU fp32 "
-                                  f"dequantise-then-matmul"}
+        cpu = CpuPath(m_full, n, k)
+        cpu.step()
+        times = []
+        t_all = time.perf_counter()
+        while len(times) < 3 or (time.perf_counter() - t_all < 10.0 and len(times) < 30):
+            times.append(cpu.step())
+        tf_cpu = 2.0 * m_full * n * k / statistics.mean(times) / 1e12
+        cpu_baseline = {"value": round(tf_cpu, 4), "unit": UNIT, "cores": cpu.threads, "kind": cpu.kind,
+                        "sample": f"{len(times)} steps; " + cpu.describe()}
 
     if rank == 0:
         line = {
@@ -401,52 +549,53 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "e4m3fn x e4m3fn -> fp32 accumulate -> bf16", "data": "synthetic",
             "config": {"workload": f"fp8_block_scaled_gemm M={m_full} N={n} K={k}",
-                       "sharding": f"{grid_m} x {grid_n} grid of row x column blocks of c: {m} rows x {n_loc} columns "
-                                   f"per GPU, no collective, c left sharded",
-                       "plan": f"{'2x' if plan.cta_pair else ''}128x{plan.block_n} split{plan.split_k} "
-                               f"stages{plan.stages} grid{plan.grid}",
+                       "sharding": f"b and b_scale cut along N over {world} GPU(s), a and a_scale replicated: {m} rows x "
+                                   f"{n_loc} columns per GPU, no collective, c left sharded",
+                       "plan": plan_text(plan),
                        "l2": f"{nsets} rotating buffer sets of {set_bytes >> 20} MiB (> 2x L2) between launches",
                        "spot_check_pass": ok},
             "pct_fp8_peak_nominal": round(100 * value / (NOMINAL_FP8_TFLOPS * world), 2),
             "roofline": {"bound": "tensor", "achieved": round(per_gpu_tflops, 2), "peak": round(fp8_peak, 1),
                          "unit": "TFLOP/s", "frac": round(per_gpu_tflops / fp8_peak, 4),
                          "peak_source": f"2 x bf16_tflops of {peaks['source']} (fp8 tcgen05 rate is twice bf16)",
-                         "traffic": HEADLINE_DRAM_BYTES if (world == 1 and not args.shape) else None,
+                         "traffic": MEASURED_DRAM_BYTES.get((m, n_loc, k)),
                          "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)",
                          "algorithmic_bytes": algorithmic_bytes(m, n_loc, k)},
+            "sustained": {"steps": sus_steps, "ms_per_step": round(sus_ms, 5),
+                          "value": round(flops / (sus_ms * 1e-3) / 1e12, 2), "unit": UNIT,
+                          "note": "the same launches back to back for at least one second (power cap settled)"},
             "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 3), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "bit_equal_to_device_path": e2e_ok},
             "gpu_launches": args.steps,
             "clocks": clocks,
         }
+        if grid_run is not None:
+            line["row_column_grid"] = grid_run
         if mn_ms is not None:
             line["mn_major_operands"] = {"ms_per_step": round(mn_ms, 5),
                                          "value": round(flops / (mn_ms * 1e-3) / 1e12, 2), "unit": UNIT}
         if grouped is not None:
             line["grouped"] = grouped
-        if gather_ms is not None:
-            line["all_gather_c"] = {"ms": round(gather_ms, 4), "bytes_per_rank": 2 * m * n_loc,
-                                    "note": "NCCL all_gather_into_tensor of the bf16 blocks into [ranks, rows, columns]; "
-                                            "outside the timed GEMM"}
+        if gather is not None:
+            line["all_gather_c"] = gather
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
         if per_shape:
             line["per_shape"] = per_shape
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    ranks.close()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    # 2000 steps of ~0.3 ms: long enough for the power cap to settle and for the clock sampler
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--no-sweep", action="store_true", help="skip the per-shape sweep (N=1 only)")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the per-shape sweep")
     ap.add_argument("--shape", default="", help="M,N,K of another workload (for small profiler captures)")
-    ap.add_argument("--grid", default="", help="ROWSxCOLS grid of the ranks (default: the cost model's choice)")
+    ap.add_argument("--grid", default="", help="ROWSxCOLS grid of the ranks for the second figure "
+                                               "(default: the cost model's choice)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

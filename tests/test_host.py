@@ -151,3 +151,7 @@ def test_runner_spec_parser_and_grid():
         runner.parse_spec("m: 8; n: 16")
     grid = runner.competition_cases()
     assert len(grid) == 18 and all(k % 128 == 0 for (_, _, k, _) in grid)
+    # two values of m times the same nine (n, k) pairs, every case with a seed of its own
+    assert sorted({m for (m, _, _, _) in grid}) == [1024, 6144]
+    assert {(n, k) for (m, n, k, _) in grid if m == 1024} == {(n, k) for (m, n, k, _) in grid if m == 6144}
+    assert len({(n, k) for (_, n, k, _) in grid}) == 9 and len({s for (*_, s) in grid}) == 18
