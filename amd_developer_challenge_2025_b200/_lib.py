@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # B200_FP8_MM_LIB selects another build of the same library (e.g. one made with extra nvcc flags).
 LIB_PATH = os.environ.get("B200_FP8_MM_LIB") or os.path.join(HERE, "lib", "libb200fp8mm.so")
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 # Every symbol include/b200_fp8_mm.h declares.
 EXPORTS = (
@@ -20,6 +20,7 @@ EXPORTS = (
     "b200_fp8_mm_grouped",
     "b200_fp8_mm_static_scratch",
     "b200_fp8_mm_static_scratch_limit",
+    "b200_fp8_mm_selftest_wait_expiry",
     "b200_fp8_mm_workspace_bytes",
     "b200_fp8_mm_plan_workspace_bytes",
     "b200_fp8_mm_describe",
@@ -81,6 +82,10 @@ def load() -> ctypes.CDLL:
     # the same argument list without the (workspace, workspace_bytes) pair
     lib.b200_fp8_mm_static_scratch.argtypes = _GEMM_ARGS[:16] + _GEMM_ARGS[18:]
     lib.b200_fp8_mm_static_scratch.restype = ctypes.c_int
+    # a .. ldc as for b200_fp8_mm, then (wait_limit_ns, skip_kblock, device_status, stream)
+    lib.b200_fp8_mm_selftest_wait_expiry.argtypes = (_GEMM_ARGS[:15] + [ctypes.c_ulonglong, ctypes.c_int,
+                                                                      ctypes.c_void_p, ctypes.c_void_p])
+    lib.b200_fp8_mm_selftest_wait_expiry.restype = ctypes.c_int
     lib.b200_fp8_mm_static_scratch_limit.argtypes = []
     lib.b200_fp8_mm_static_scratch_limit.restype = ctypes.c_size_t
     lib.b200_fp8_mm_workspace_bytes.argtypes = [ctypes.c_int] * 3

@@ -50,6 +50,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "b200_fp8_mm.h"
 
 namespace {
@@ -57,7 +60,7 @@ namespace {
 constexpr int kBlockM = 128;  // rows of C per CTA
 constexpr int kBlockK = 128;  // bytes of e4m3 per row of a stage = one scale block = one 128B swizzle row
 constexpr int kMmasPerBlock = 4;  // K = 32 per instruction
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // default limit of every mbarrier wait: 2 s
 constexpr int kCounterBytes = 4096;
 constexpr int kMaxCounters = kCounterBytes / 4;
 constexpr int kMaxStages = 8;
@@ -87,7 +90,7 @@ struct KernelParams {
   int stages;
   int tmem_bufs;  // TMEM partial buffers in use: divides stages, at most TileCfg::kTmemBufs
   int issuers;     // MMA-issuing threads in use: 1 or 2
-  int store_bufs;  // staging buffers per promotion warpgroup for the TMA store of c: 0 (plain stores), 1 or 2
+  int store_bufs;  // staging buffers per promotion warpgroup for the TMA store of c: 0 (plain stores), 1 .. 4
   // Operand layout, as the values the producer and the MMA threads need (see OperandLayout below).
   int a_mn, b_mn;            // 1: the operand is MN-major in global and shared memory
   int b_boxes;               // TMA boxes per stage of b (1 when K-major)
@@ -100,6 +103,11 @@ struct KernelParams {
   int groups;
   const int* m_valid;        // device int[groups]: rows of each group that exist (null: all M)
   long long sa_g, sb_g, c_g; // group strides of a_scale, b_scale (floats) and c (elements)
+  unsigned long long wait_limit_ns;  // every mbarrier wait gives up after this long
+  // Self-test of the give-up path (b200_fp8_mm_selftest_wait_expiry): the producer of the plain 64-wide
+  // single-CTA kernel leaves this K block of the launch's first tile out (no expect_tx, no copy), so the waits
+  // that depend on it run into the limit. -1 in every other launch.
+  int selftest_skip_kblock;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -184,18 +192,19 @@ __device__ __forceinline__ unsigned long long global_ns() {
 struct AbortCtx {
   volatile int* abort_flag;  // shared memory
   int* status;               // global, may be null
+  unsigned long long limit_ns;
 };
 
 // Bounded wait. Returns false when the wait expired here or in another role.
 __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                               int where) {
+                                               unsigned long long limit_ns, int where) {
   const unsigned long long t0 = global_ns();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3u) == 0) {
       if (*abort_flag) return false;
-      if (global_ns() - t0 > kWaitLimitNs) {
+      if (global_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (status != nullptr) {
           if (atomicCAS(status, 0, B200_FP8_MM_DEV_WAIT_EXPIRED) == 0) {
@@ -212,7 +221,7 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, vo
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, ctx.abort_flag, ctx.status, where);
+  return mbar_wait_slow(bar, parity, ctx.abort_flag, ctx.status, ctx.limit_ns, where);
 }
 
 // TMA tile load into this CTA's shared memory; completion bytes go to `bar`.
@@ -621,13 +630,17 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 
   const int warp = static_cast<int>(threadIdx.x) >> 5;
   const int lane = static_cast<int>(threadIdx.x) & 31;
-  const AbortCtx ctx{abort_flag, p.status};
+  const AbortCtx ctx{abort_flag, p.status, p.wait_limit_ns};
   const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
       // one arrive.expect_tx per producing CTA + one release per promotion warp (of both CTAs)
+#ifdef FP8MM_X_FREERUN
+      mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1));
+#else
       mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1) * (1 + (Cfg::kHalf ? Cfg::kEpiWarps / 2 : Cfg::kEpiWarps)));
+#endif
       mbar_init(smem_u32(&done_bar[s]), 1);  // the MMA thread's commit
       if constexpr (Cfg::kHalf) {
         mbar_init(smem_u32(&done_lo_bar[s]), 1);
@@ -695,8 +708,25 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               ok = false;
               break;
             }
+            if constexpr (BN == 64 && !PAIR && !GENERIC) {
+              if (kb == p.selftest_skip_kblock && w == work_begin()) {  // self-test only: this block never arrives
+                if (++stage == stages) {
+                  stage = 0;
+                  phase ^= 1u;
+                }
+                continue;
+              }
+            }
             // Both CTAs of a pair report to the leader's barrier: its MMA thread consumes the stage.
             const uint32_t fb = PAIR ? map_to_cta(smem_u32(&full_bar[stage]), 0) : smem_u32(&full_bar[stage]);
+#ifdef FP8MM_X_NOTMA
+            mbar_expect_tx_cluster(fb, 0);
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+#endif
             mbar_expect_tx_cluster(fb, Cfg::kStageBytes);
             const uint32_t sa = smem_u32(ring + stage * Cfg::kStageBytes);
             // K-major: x = byte of K, y = matrix row. MN-major: x = matrix row (a multiple of 64), y = k.
@@ -730,6 +760,12 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               phase ^= 1u;
             }
           }
+        }
+        if (!ok || *abort_flag) {
+          // Some wait ran out. Copies this thread issued may still be landing in shared memory: give them far
+          // longer than a copy takes (a bounded pause, not a wait on anything) before the CTA is torn down.
+          const unsigned long long t0 = global_ns();
+          while (global_ns() - t0 < 100000ull) __nanosleep(2000);
         }
       }
       __syncwarp();
@@ -771,11 +807,13 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               break;
             }
             tcgen05_fence_after();
+#ifndef FP8MM_X_NOMMA
 #pragma unroll
             for (int k = 0; k < kMmasPerBlock; ++k) {
               // next K=32 slice: 32 bytes further inside the swizzle row (K-major) or 32 rows further
               umma_f8<PAIR>(d_addr, a_lo + a_kstep * k, b_lo + b_kstep * k, a_hi, b_hi, idesc, k > 0 ? 1u : 0u);
             }
+#endif
             if constexpr (Cfg::kHalf) {
               umma_commit<PAIR>(smem_u32(&done_lo_bar[my_stage]));
               // columns 128-255: the same A, the second 64 rows of each CTA's share of B
@@ -873,6 +911,9 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     const uint32_t full_base = PAIR ? map_to_cta(rel_local, 0) : rel_local;
     const uint32_t ready_base = (Cfg::kHalf && half == 0) ? smem_u32(&done_lo_bar[0]) : smem_u32(&done_bar[0]);
     auto release_to = [&](int st) {
+#ifdef FP8MM_X_FREERUN
+      return;
+#endif
       if (lane == 0) {
         if constexpr (PAIR) {
           mbar_arrive_cluster(full_base + static_cast<uint32_t>(st * 8));
@@ -890,7 +931,11 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     uint32_t cphase = 0, sphase = 0;
     bool ok = true;
 
-    for (int w = work_begin(); w < total_work && ok; w += work_step) {
+    // `ok` turns false when a wait of this warp ran out (or another role's did: the shared abort flag). The
+    // warp then stops waiting, fetching and storing but still walks the remaining tiles and takes part in
+    // every named barrier of their epilogues, so that warps which have not noticed yet are never left alone
+    // at a barrier; they notice at their next wait.
+    for (int w = work_begin(); w < total_work; w += work_step) {
       const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
       if (it.skip) continue;
       const int row = it.m0 + static_cast<int>(cta_rank) * kBlockM + row_in_tile;
@@ -911,7 +956,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       for (int kb0 = it.kb_begin; kb0 < it.kb_end && ok; kb0 += kScaleGroup) {
         // Scales of the next (up to) four K blocks: three 16-byte shared-memory loads, then the
         // slot goes back to the loader.
-        if (!mbar_wait(smem_u32(&scale_full_bar[slot]), sphase, ctx, 0x600 | slot)) {
+        // (the vote makes the outcome the same in every lane: the warp-wide TMEM fetches below need all 32)
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&scale_full_bar[slot]), sphase, ctx, 0x600 | slot))) {
           ok = false;
           break;
         }
@@ -932,7 +978,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         for (int u = 0; u < kScaleGroup; ++u) {
           if (kb0 + u >= it.kb_end) break;
           if (!(Cfg::kEarlyProbe && ready_next)) {
-            if (!mbar_wait(ready_base + static_cast<uint32_t>(cstage * 8), cphase, ctx, 0x400 | cstage)) {
+            if (!__all_sync(0xffffffffu,
+                            mbar_wait(ready_base + static_cast<uint32_t>(cstage * 8), cphase, ctx, 0x400 | cstage))) {
               ok = false;
               break;
             }
@@ -941,10 +988,17 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(buf * BN + col_base);
           constexpr int CC = Cfg::kChunkCols;
           uint32_t v[CC];
+#ifdef FP8MM_X_NOPROMO
+#pragma unroll
+          for (int j = 0; j < CC; ++j) v[j] = 0;
+#else
           tmem_ld(taddr, v);
+#endif
 #pragma unroll
           for (int ch = 0; ch < Cfg::kChunks; ++ch) {
+#ifndef FP8MM_X_NOPROMO
             tmem_ld_wait(v);
+#endif
             if (ch + 1 == Cfg::kChunks) {
               // Every column of this buffer is in registers (tcgen05.wait::ld has returned in every
               // lane once __syncwarp is passed): hand it back to the MMA warp.
@@ -962,6 +1016,9 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               }
             }
             // 32 columns at a time: a scale-row boundary can fall on any multiple of 32 columns
+#ifdef FP8MM_X_NOPROMO
+            if (ch > 0) continue;
+#endif
 #pragma unroll
             for (int q = 0; q < CC / 32; ++q) {
               const int cb = ch * CC + 32 * q;  // offset inside this thread's columns
@@ -976,7 +1033,9 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                   accf[cb - kPackedCols + j] = fmaf(__uint_as_float(v[32 * q + j]), s, accf[cb - kPackedCols + j]);
               }
             }
+#ifndef FP8MM_X_NOPROMO
             if (ch + 1 < Cfg::kChunks) tmem_ld(taddr + static_cast<uint32_t>((ch + 1) * CC), v);
+#endif
           }
           if (++buf == nbufs) buf = 0;
           if (++cstage == stages) {
@@ -985,8 +1044,6 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           }
         }
       }
-      if (!ok) break;
-
       float2 acc[Cfg::kColsPerThread / 2];
 #pragma unroll
       for (int j = 0; j < Cfg::kColsPerThread / 2; ++j) {
@@ -1001,7 +1058,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         }
       }
       const int col0 = it.n0 + col_base;  // first column of this thread inside (the shard of) c
-      bool do_store = true;
+      bool do_store = true;  // the same in every promotion thread of the CTA
       if (it.nsplit > 1) {
         // Split-K: publish this K range's fp32 tile; the last CTA to arrive for the tile then sums the
         // ranges in order 0..nsplit-1 (so the result does not depend on arrival order) and stores the
@@ -1020,9 +1077,12 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         __threadfence();
         epi_bar_sync<Cfg::kEpiThreads>();
         if (epi_tid == 0) {
-          const int prev = atomicAdd(p.counters + unit, 1);
-          const int last = (prev == it.nsplit - 1) ? 1 : 0;
-          if (last) p.counters[unit] = 0;  // leave the counters zero for the next launch
+          int last = 0;
+          if (*abort_flag == 0) {
+            const int prev = atomicAdd(p.counters + unit, 1);
+            last = (prev == it.nsplit - 1) ? 1 : 0;
+            if (last) p.counters[unit] = 0;  // leave the counters zero for the next launch
+          }
           *last_flag = last;
         }
         epi_bar_sync<Cfg::kEpiThreads>();
@@ -1057,18 +1117,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const int wg_tid = epi_tid & 127;
         uint8_t* my_stage = staging + half * p.store_bufs * kStoreBufBytes;
         const int sw = (row_in_tile >> 1) & 3;
-#pragma unroll
-        for (int ch = 0; ch < Cfg::kColsPerThread / kStoreBoxCols; ++ch) {
-          const int bufi = (p.store_bufs == 2) ? (ch & 1) : 0;
-          // the store that last used this buffer has finished reading it
-          if (wg_tid == 0) {
-            if (p.store_bufs == 2) {
-              tma_store_wait_read<1>();
-            } else {
-              tma_store_wait_read<0>();
-            }
-          }
-          wg_bar_sync(half);
+        constexpr int kBoxes = Cfg::kColsPerThread / kStoreBoxCols;
+        auto stage_box = [&](int ch, int bufi) {
           uint8_t* rowp = my_stage + bufi * kStoreBufBytes + row_in_tile * 64;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -1080,19 +1130,50 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             o.w = pack_bf16x2(acc[j + 3].x, acc[j + 3].y);
             *reinterpret_cast<uint4*>(rowp + ((q ^ sw) << 4)) = o;
           }
+        };
+        auto store_box = [&](int ch, int bufi) {
+          if (GENERIC && p.groups > 0) {
+            tma_store_3d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
+                         it.m0 + static_cast<int>(cta_rank) * kBlockM, it.group);
+          } else {
+            tma_store_2d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
+                         it.m0 + static_cast<int>(cta_rank) * kBlockM);
+          }
+        };
+        if (p.store_bufs >= kBoxes) {
+          // A staging buffer for every box of the warpgroup's share: the whole share is staged between two
+          // barriers and leaves as kBoxes bulk stores that drain while the next tile's K loop runs; the
+          // wait below is for the previous tile's stores, issued a tile ago.
+          if (wg_tid == 0) tma_store_wait_read<0>();
+          wg_bar_sync(half);
+#pragma unroll
+          for (int ch = 0; ch < kBoxes; ++ch) stage_box(ch, ch);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           wg_bar_sync(half);
-          if (wg_tid == 0) {
-            if (GENERIC && p.groups > 0) {
-              tma_store_3d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
-                           it.m0 + static_cast<int>(cta_rank) * kBlockM, it.group);
-            } else {
-              tma_store_2d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
-                           it.m0 + static_cast<int>(cta_rank) * kBlockM);
+          if (wg_tid == 0 && *abort_flag == 0) {
+#pragma unroll
+            for (int ch = 0; ch < kBoxes; ++ch) store_box(ch, ch);
+          }
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < kBoxes; ++ch) {
+            const int bufi = (p.store_bufs == 2) ? (ch & 1) : 0;
+            // the store that last used this buffer has finished reading it
+            if (wg_tid == 0) {
+              if (p.store_bufs == 2) {
+                tma_store_wait_read<1>();
+              } else {
+                tma_store_wait_read<0>();
+              }
             }
+            wg_bar_sync(half);
+            stage_box(ch, bufi);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            wg_bar_sync(half);
+            if (wg_tid == 0 && *abort_flag == 0) store_box(ch, bufi);
           }
         }
-      } else if (do_store) {
+      } else if (do_store && ok) {
         if (row < it.m_limit) {
           __nv_bfloat16* crow = p.c + static_cast<long long>(it.group) * p.c_g + static_cast<long long>(row) * p.ldc;
 #pragma unroll
@@ -1149,6 +1230,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// The only mutable state of the library's host side: per-device facts looked up once (SM count, kernels
+// opted in to the large shared-memory carve-out, address of the built-in scratch array) and the cache of
+// encoded tensor maps. All of it is guarded by this mutex, so entry points may be called from several threads.
+std::mutex g_host_mutex;
+
 EncodeTiledFn get_encode_fn() {
   static EncodeTiledFn fn = []() -> EncodeTiledFn {
     void* ptr = nullptr;
@@ -1162,71 +1248,147 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Everything a tiled tensor map is made from. A map is a pure function of these values (it holds the base
+// address, not the memory), so an encoded map is kept and handed out again for the same key: the weights of
+// a layer, and any buffer a caller reuses, are encoded once instead of on every call (the driver's encoder
+// costs the host about as much as a small GEMM runs on the device).
+struct MapKey {
+  const void* base;
+  cuuint64_t dims[3];
+  cuuint64_t strides[2];
+  cuuint32_t box[3];
+  int rank;
+  int dtype;
+  int swizzle;
+  int l2;
+  bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    const unsigned char* p = reinterpret_cast<const unsigned char*>(&k);
+    uint64_t h = 1469598103934665603ull;  // FNV-1a over the key's bytes
+    for (size_t i = 0; i < sizeof(MapKey); ++i) h = (h ^ p[i]) * 1099511628211ull;
+    return static_cast<size_t>(h);
+  }
+};
+
+constexpr size_t kMapCacheEntries = 4096;  // the cache is emptied when it reaches this size
+
+bool encode_map(CUtensorMap* map, const MapKey& key_in) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  MapKey key;
+  memset(&key, 0, sizeof(key));  // padding bytes take part in the comparison
+  key.base = key_in.base;
+  for (int i = 0; i < 3; ++i) {
+    key.dims[i] = key_in.dims[i];
+    key.box[i] = key_in.box[i];
+  }
+  key.strides[0] = key_in.strides[0];
+  key.strides[1] = key_in.strides[1];
+  key.rank = key_in.rank;
+  key.dtype = key_in.dtype;
+  key.swizzle = key_in.swizzle;
+  key.l2 = key_in.l2;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  {
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *map = it->second;
+      return true;
+    }
+  }
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = fn(map, static_cast<CUtensorMapDataType>(key.dtype), static_cast<cuuint32_t>(key.rank),
+                        const_cast<void*>(key.base), key.dims, key.strides, key.box, elem_strides,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, static_cast<CUtensorMapSwizzle>(key.swizzle),
+                        static_cast<CUtensorMapL2promotion>(key.l2), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+  if (cache.size() >= kMapCacheEntries) cache.clear();
+  cache.emplace(key, *map);
+  return true;
+}
+
 // e4m3 matrix of `rows` rows (M or N) and K columns. K-major (K contiguous, row pitch ld): box = 128 bytes of
 // K x box_rows rows, 128-byte swizzle. MN-major (rows contiguous, ld bytes between consecutive k): box =
 // box_rows (128 or 64) bytes of rows x 128 k, swizzle span = the box's inner extent.
 bool encode_operand_map(CUtensorMap* map, const void* base, int rows, int K, long long ld, int box_rows,
                         bool mn_major) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(mn_major ? rows : K),
-                              static_cast<cuuint64_t>(mn_major ? K : rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(mn_major ? box_rows : kBlockK),
-                             static_cast<cuuint32_t>(mn_major ? kBlockK : box_rows)};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  const CUtensorMapSwizzle swz =
-      (mn_major && box_rows == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  MapKey k;
+  memset(&k, 0, sizeof(k));
+  k.base = base;
+  k.rank = 2;
+  k.dims[0] = static_cast<cuuint64_t>(mn_major ? rows : K);
+  k.dims[1] = static_cast<cuuint64_t>(mn_major ? K : rows);
+  k.strides[0] = static_cast<cuuint64_t>(ld);
+  k.box[0] = static_cast<cuuint32_t>(mn_major ? box_rows : kBlockK);
+  k.box[1] = static_cast<cuuint32_t>(mn_major ? kBlockK : box_rows);
+  k.dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  k.swizzle = (mn_major && box_rows == 64) ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  k.l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+  return encode_map(map, k);
 }
 
 // bf16 matrix c [M, N] with N contiguous: box = 32 columns (64 bytes) x 128 rows, 64-byte swizzle.
 bool encode_output_map(CUtensorMap* map, void* base, int M, int N, long long ldc) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldc) * 2};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kStoreBoxCols), static_cast<cuuint32_t>(kBlockM)};
-  const cuuint32_t elem_strides[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, elem_strides,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  MapKey k;
+  memset(&k, 0, sizeof(k));
+  k.base = base;
+  k.rank = 2;
+  k.dims[0] = static_cast<cuuint64_t>(N);
+  k.dims[1] = static_cast<cuuint64_t>(M);
+  k.strides[0] = static_cast<cuuint64_t>(ldc) * 2;
+  k.box[0] = static_cast<cuuint32_t>(kStoreBoxCols);
+  k.box[1] = static_cast<cuuint32_t>(kBlockM);
+  k.dtype = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  k.swizzle = CU_TENSOR_MAP_SWIZZLE_64B;
+  k.l2 = CU_TENSOR_MAP_L2_PROMOTION_NONE;
+  return encode_map(map, k);
 }
 
 // Grouped operands: e4m3 [groups][rows][K] with K contiguous, row pitch ld and group pitch lg (bytes);
 // box = 128 bytes of K x box_rows rows of one group.
 bool encode_operand_map_3d(CUtensorMap* map, const void* base, int groups, int rows, int K, long long ld,
                            long long lg, int box_rows) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows),
-                              static_cast<cuuint64_t>(groups)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld), static_cast<cuuint64_t>(lg)};
-  const cuuint32_t box[3] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows), 1};
-  const cuuint32_t elem_strides[3] = {1, 1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box,
-                        elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  MapKey k;
+  memset(&k, 0, sizeof(k));
+  k.base = base;
+  k.rank = 3;
+  k.dims[0] = static_cast<cuuint64_t>(K);
+  k.dims[1] = static_cast<cuuint64_t>(rows);
+  k.dims[2] = static_cast<cuuint64_t>(groups);
+  k.strides[0] = static_cast<cuuint64_t>(ld);
+  k.strides[1] = static_cast<cuuint64_t>(lg);
+  k.box[0] = static_cast<cuuint32_t>(kBlockK);
+  k.box[1] = static_cast<cuuint32_t>(box_rows);
+  k.box[2] = 1;
+  k.dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  k.swizzle = CU_TENSOR_MAP_SWIZZLE_128B;
+  k.l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+  return encode_map(map, k);
 }
 
 // Grouped output: bf16 [groups][M][N]; rows past M of a group are clipped by the store.
 bool encode_output_map_3d(CUtensorMap* map, void* base, int groups, int M, int N, long long ldc, long long c_g) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M),
-                              static_cast<cuuint64_t>(groups)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ldc) * 2, static_cast<cuuint64_t>(c_g) * 2};
-  const cuuint32_t box[3] = {static_cast<cuuint32_t>(kStoreBoxCols), static_cast<cuuint32_t>(kBlockM), 1};
-  const cuuint32_t elem_strides[3] = {1, 1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, elem_strides,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  MapKey k;
+  memset(&k, 0, sizeof(k));
+  k.base = base;
+  k.rank = 3;
+  k.dims[0] = static_cast<cuuint64_t>(N);
+  k.dims[1] = static_cast<cuuint64_t>(M);
+  k.dims[2] = static_cast<cuuint64_t>(groups);
+  k.strides[0] = static_cast<cuuint64_t>(ldc) * 2;
+  k.strides[1] = static_cast<cuuint64_t>(c_g) * 2;
+  k.box[0] = static_cast<cuuint32_t>(kStoreBoxCols);
+  k.box[1] = static_cast<cuuint32_t>(kBlockM);
+  k.box[2] = 1;
+  k.dtype = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  k.swizzle = CU_TENSOR_MAP_SWIZZLE_64B;
+  k.l2 = CU_TENSOR_MAP_L2_PROMOTION_NONE;
+  return encode_map(map, k);
 }
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -1271,10 +1433,19 @@ int max_stages_for(int block_n, int pair, int store_bufs) {
   return s;
 }
 
-// Staging buffers for the TMA store of c: two (the store of one box overlaps the staging of the next)
-// unless that would leave fewer than four ring stages.
+// Staging buffers per warpgroup for the TMA store of c. Short K (a tile is only a few K blocks long, so the
+// epilogue is a large share of it and the ring need not be deep): one buffer for every 32-column box of the
+// warpgroup's share, so that the whole tile is staged at once and its stores drain under the next tile.
+// Otherwise two (the store of one box overlaps the staging of the next) unless that would leave fewer than
+// four ring stages.
+int store_boxes_per_group(int block_n) { return block_n / (epi_warps_for(block_n) / 4) / kStoreBoxCols; }
+
 int store_bufs_for(int block_n, int pair, int kblocks_per_item) {
-  if (kblocks_per_item <= 8) return 2;
+  if (kblocks_per_item <= 8) {
+    const int all = store_boxes_per_group(block_n);
+    if (max_stages_for(block_n, pair, all) >= (kblocks_per_item < 4 ? kblocks_per_item : 4)) return all;
+    return 2 < all ? 2 : all;
+  }
   // measured: a second staging buffer is worth more than a fifth (single CTA) or seventh (pair) ring stage
   const int with_two = max_stages_for(block_n, pair, 2);
   return (with_two >= 4 || with_two == max_stages_for(block_n, pair, 1)) ? 2 : 1;
@@ -1411,7 +1582,7 @@ bool plan_is_supported(const b200_fp8_mm_plan& pl, int kblocks) {
   if (!valid_block_n(pl.block_n)) return false;
   if (pl.cta_pair != 0 && pl.cta_pair != 1) return false;
   if (pl.stages < 2 || pl.stages > kMaxStages) return false;
-  if (pl.store_bufs < 0 || pl.store_bufs > 2) return false;
+  if (pl.store_bufs < 0 || pl.store_bufs > 4) return false;
   if (pl.smem_bytes > kMaxSmem) return false;
   if (pl.split_k < 1 || pl.split_k > kblocks) return false;
   if (pl.split_k > 1 && (pl.tiles - pl.full_tiles) * (pl.cta_pair ? 2 : 1) > kMaxCounters) return false;
@@ -1448,10 +1619,11 @@ KernelFn kernel_for(int block_n, int pair, bool generic) {
 }
 
 int device_sm_count() {
-  // Cached per process for the current device at first use; B200 has 148.
+  // Looked up once per device (the current one) and kept; B200 has 148.
   static int cached[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
   if (cached[dev] == 0) {
     int n = 0, major = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
@@ -1460,6 +1632,14 @@ int device_sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+// SM count the size functions plan for: the current device's when there is one (so that the size matches the
+// plan b200_fp8_mm will make on it), else B200's 148.
+int sm_count_for_sizing() {
+  const int n = device_sm_count();
+  if (n <= 0) (void)cudaGetLastError();
+  return n > 0 ? n : 148;
 }
 
 int launch(KernelFn fn, const b200_fp8_mm_plan& pl, const CUtensorMap& map_a, const CUtensorMap& map_b,
@@ -1480,10 +1660,17 @@ bool classify_operand(long long s_row, long long s_k, int rows, int K, bool* mn_
   return (*ld % 16) == 0;
 }
 
+// What the special-purpose entry points change about a run.
+struct RunOptions {
+  bool zero_counters = false;                       // clear the workspace's tile counters on the stream, once every check has passed
+  unsigned long long wait_limit_ns = kWaitLimitNs;  // limit of every mbarrier wait in the kernel
+  int selftest_skip_kblock = -1;                    // see KernelParams::selftest_skip_kblock
+};
+
 int run(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int M, int N, int K,
         long long a_sm, long long a_sk, long long b_sn, long long b_sk, long long sa_m, long long sa_k,
         long long sb_n, long long sb_k, long long ldc, int n_phase, void* workspace, size_t workspace_bytes,
-        int* device_status, void* stream, const b200_fp8_mm_plan* forced_in) {
+        int* device_status, void* stream, const b200_fp8_mm_plan* forced_in, const RunOptions& opts = RunOptions()) {
   if (a == nullptr || b == nullptr || a_scale == nullptr || b_scale == nullptr || c == nullptr)
     return B200_FP8_MM_ERR_NULL;
   if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return B200_FP8_MM_ERR_SHAPE;
@@ -1589,7 +1776,16 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   kp.b_scale_rows = ceil_div(N + n_phase, 128);
   kp.vec_store =
       ((reinterpret_cast<uintptr_t>(c) % 16) == 0 && (ldc % 8) == 0 && (N % 8) == 0) ? 1 : 0;
+  kp.wait_limit_ns = opts.wait_limit_ns;
+  kp.selftest_skip_kblock = opts.selftest_skip_kblock;
 
+  if (opts.zero_counters && need > 0) {
+    // Nothing has been put on the stream before this point: a call that is refused leaves the stream untouched.
+    if (cudaMemsetAsync(workspace, 0, kCounterBytes, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return B200_FP8_MM_ERR_LAUNCH;
+    }
+  }
   return launch(fn, pl, map_a, map_b, map_c, kp, stream);
 }
 
@@ -1603,6 +1799,7 @@ int launch(KernelFn fn, const b200_fp8_mm_plan& pl, const CUtensorMap& map_a, co
     (void)cudaGetDevice(&dev);
     const bool generic = kp.groups > 0 || kp.a_mn || kp.b_mn;
     const int slot = (generic ? 8 : 0) + (pl.block_n / 64 - 1) * 2 + (pl.cta_pair ? 1 : 0);
+    std::lock_guard<std::mutex> lock(g_host_mutex);
     if (dev < 0 || dev >= 64 || !opted_in[dev][slot]) {
       err = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kMaxSmem);
@@ -1738,6 +1935,8 @@ int run_grouped(const void* a, const void* b, const float* a_scale, const float*
   }
   kp.b_scale_rows = ceil_div(N, 128);
   kp.vec_store = ((reinterpret_cast<uintptr_t>(c) % 16) == 0 && (ldc % 8) == 0 && (c_g % 8) == 0 && (N % 8) == 0) ? 1 : 0;
+  kp.wait_limit_ns = kWaitLimitNs;
+  kp.selftest_skip_kblock = -1;
   kp.groups = groups;
   kp.m_valid = m_valid;
   kp.sa_g = sa_g;
@@ -1773,6 +1972,7 @@ int static_scratch_address(void** out) {
   static void* cached[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_FP8_MM_ERR_DRIVER;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
   if (cached[dev] == nullptr) {
     void* ptr = nullptr;
     const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
@@ -1828,16 +2028,34 @@ int b200_fp8_mm_static_scratch(const void* a, const void* b, const float* a_scal
   void* scratch = nullptr;
   const int rc = static_scratch_address(&scratch);  // first call on a device looks the address up
   if (rc != B200_FP8_MM_OK) return rc;
-  if (need > 0) {
-    // The array still holds whatever the previous call left; the tile counters have to start at
-    // zero (a launch that was cut short would leave them mid-count).
-    if (cudaMemsetAsync(scratch, 0, kCounterBytes, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return B200_FP8_MM_ERR_LAUNCH;
-    }
-  }
+  // The array still holds whatever the previous call left; the tile counters have to start at zero (a launch
+  // that was cut short would leave them mid-count). run() clears them on the stream, after its own checks.
+  RunOptions opts;
+  opts.zero_counters = true;
   return run(a, b, a_scale, b_scale, c, M, N, K, lda, 1, ldb, 1, sa_m, sa_k, sb_n, sb_k, ldc, n_phase, scratch,
-             kStaticScratchBytes, device_status, stream, nullptr);
+             kStaticScratchBytes, device_status, stream, nullptr, opts);
+}
+
+int b200_fp8_mm_selftest_wait_expiry(const void* a, const void* b, const float* a_scale, const float* b_scale,
+                                     void* c, int M, int N, int K, long long lda, long long ldb, long long sa_m,
+                                     long long sa_k, long long sb_n, long long sb_k, long long ldc,
+                                     unsigned long long wait_limit_ns, int skip_kblock, int* device_status,
+                                     void* stream) {
+  if (device_status == nullptr) return B200_FP8_MM_ERR_NULL;
+  if (K <= 0 || (K % kBlockK) != 0 || skip_kblock < 0 || skip_kblock >= K / kBlockK) return B200_FP8_MM_ERR_SHAPE;
+  // A wait that runs out must do so soon (the GPU is busy until then) but not so soon that a healthy wait
+  // could be mistaken for a dead one.
+  if (wait_limit_ns < 1000000ull || wait_limit_ns > 100000000ull) return B200_FP8_MM_ERR_PLAN;
+  b200_fp8_mm_plan forced;
+  memset(&forced, 0, sizeof(forced));
+  forced.block_n = 64;   // the only kernel that honours skip_kblock
+  forced.cta_pair = -1;
+  forced.split_k = 1;
+  RunOptions opts;
+  opts.wait_limit_ns = wait_limit_ns;
+  opts.selftest_skip_kblock = skip_kblock;
+  return run(a, b, a_scale, b_scale, c, M, N, K, lda, 1, ldb, 1, sa_m, sa_k, sb_n, sb_k, ldc, 0, nullptr, 0,
+             device_status, stream, &forced, opts);
 }
 
 int b200_fp8_mm_grouped(const void* a, const void* b, const float* a_scale, const float* b_scale, void* c, int groups,
@@ -1855,11 +2073,12 @@ size_t b200_fp8_mm_workspace_bytes(int M, int N, int K) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return 0;
   // Covers both the plan for K-major operands and the one for MN-major operands (no CTA pairs).
   b200_fp8_mm_plan pl, single;
-  choose_plan(M, N, K, 148, nullptr, &pl);
+  const int sms = sm_count_for_sizing();
+  choose_plan(M, N, K, sms, nullptr, &pl);
   memset(&single, 0, sizeof(single));
   single.cta_pair = -1;
   b200_fp8_mm_plan pl2;
-  choose_plan(M, N, K, 148, &single, &pl2);
+  choose_plan(M, N, K, sms, &single, &pl2);
   size_t need = plan_workspace_bytes(pl);
   if (plan_workspace_bytes(pl2) > need) need = plan_workspace_bytes(pl2);
   return ((need + 255) / 256) * 256;
@@ -1868,7 +2087,7 @@ size_t b200_fp8_mm_workspace_bytes(int M, int N, int K) {
 size_t b200_fp8_mm_plan_workspace_bytes(int M, int N, int K, const b200_fp8_mm_plan* forced) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % kBlockK) != 0) return 0;
   b200_fp8_mm_plan pl;
-  choose_plan(M, N, K, 148, forced, &pl);
+  choose_plan(M, N, K, sm_count_for_sizing(), forced, &pl);
   const size_t need = plan_workspace_bytes(pl);
   return ((need + 255) / 256) * 256;
 }
@@ -1907,6 +2126,6 @@ const char* b200_fp8_mm_strerror(int code) {
   }
 }
 
-int b200_fp8_mm_abi_version(void) { return 6; }
+int b200_fp8_mm_abi_version(void) { return 7; }
 
 }  // extern "C"

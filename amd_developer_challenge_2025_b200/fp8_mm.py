@@ -199,6 +199,35 @@ def fp8_mm(a, b, a_scale, b_scale, c, n_phase: int = 0, plan: Plan | None = None
     return c
 
 
+def selftest_wait_expiry(device="cuda", limit_ms: float = 5.0):
+    """Diagnostics: makes one wait inside the kernel run out on purpose, in the allowed way. A 128 x 64 x 256
+    problem is launched with every wait limited to `limit_ms` and with the copy of its second K block left
+    out; the kernel gives up that wait, returns by itself and reports it. Returns the four status words
+    [code, role/barrier, block, phase]; code 1 is WAIT_EXPIRED. The status words are cleared again, so the
+    next launch starts clean."""
+    from .inputs import make_inputs
+
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        a, b, a_s, b_s, c = make_inputs(128, 64, 256, seed=1, device=dev)
+        st = _status_words(dev)
+        torch.cuda.synchronize(dev)
+        rc = lib.b200_fp8_mm_selftest_wait_expiry(
+            a.data_ptr(), b.data_ptr(), a_s.data_ptr(), b_s.data_ptr(), c.data_ptr(), 128, 64, 256,
+            a.stride(0), b.stride(0), a_s.stride(0), a_s.stride(1), b_s.stride(0), b_s.stride(1), c.stride(0),
+            int(limit_ms * 1e6), 1, st.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+        if rc != 0:
+            raise Fp8MmError(rc, "selftest_wait_expiry")
+        torch.cuda.synchronize(dev)
+        words = st.tolist()
+        st.zero_()
+        torch.cuda.synchronize(dev)
+    return words
+
+
 def fp8_mm_grouped(a, b, a_scale, b_scale, c, m_valid=None, plan: Plan | None = None, check: bool = False):
     """c[g] (bf16 [G,M,N]) = block-scaled a[g] ([G,M,K]) @ b[g]^T ([G,N,K]) for every group g in one launch.
 

@@ -12,8 +12,17 @@
  * tensor cores, and the scaled blocks accumulated in fp32
  * (1-amd-fp8-mm/amd-fp8-mm-submission.py:302-357 is the reference loop).
  *
- * Every entry point takes plain pointers and sizes. The library owns no device
- * memory and allocates none; the caller supplies the workspace.
+ * Every entry point takes plain pointers and sizes. No entry point ever calls
+ * cudaMalloc or cudaFree: scratch for split-K plans is a workspace the caller
+ * supplies. The library's device image does carry one fixed 8 MiB array (used only
+ * by b200_fp8_mm_static_scratch), which the CUDA runtime materialises on each GPU
+ * when the module is loaded there, i.e. during the first call of any entry point on
+ * that GPU; make one warm-up call per device at start-up (outside stream capture) to
+ * keep module load and address lookup out of latency-critical code.
+ *
+ * Host-side state: per-device facts looked up once and a cache of encoded TMA
+ * tensor maps keyed by (pointer, extents, strides, box); both are guarded by a
+ * mutex, so the entry points may be called from several host threads.
  */
 #ifndef B200_FP8_MM_H_
 #define B200_FP8_MM_H_
@@ -42,9 +51,12 @@ enum {
 };
 
 /* Device-side status word values (written to device_status[0]; [1] holds the
- * role and barrier that gave up, [2] the block index). A kernel never traps and
- * never spins without limit: a wait that expires records one of these and every
- * role leaves its loop. */
+ * role and barrier that gave up, [2] the block index, [3] the barrier phase). A
+ * kernel never traps and never spins without limit: a wait that expires (2 s)
+ * records one of these and every role leaves its loop. After a
+ * B200_FP8_MM_DEV_WAIT_EXPIRED the output is not valid and a split-K launch may
+ * have left the workspace's tile counters mid-count: zero the workspace's first
+ * 4096 bytes (and device_status) before the next call that uses them. */
 enum {
   B200_FP8_MM_DEV_OK = 0,
   B200_FP8_MM_DEV_WAIT_EXPIRED = 1
@@ -196,8 +208,9 @@ int b200_fp8_mm_grouped(const void* a, const void* b, const float* a_scale, cons
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
  * with that device current) and keeps it; make that first call outside any stream capture.
- * All calls share the one array, which keeps what the previous call left in it: the entry
- * point zeroes the tile counters on `stream` before each launch that uses them, and two calls
+ * All calls share the one array, which keeps what the previous call left in it: once every
+ * argument check has passed, the entry point zeroes the tile counters on `stream` right before
+ * a launch that uses them (a refused call puts nothing on the stream), and two calls
  * that can overlap on the GPU (different streams, no dependency) would race on it - serialise
  * them, or use b200_fp8_mm with separate workspaces.
  */
@@ -209,11 +222,31 @@ int b200_fp8_mm_static_scratch(const void* a, const void* b, const float* a_scal
                                long long ldc, int n_phase,
                                int* device_status, void* stream);
 
+/*
+ * Self-test of the bounded waits (diagnostics; no counterpart in the reference, whose kernels
+ * have no waits to bound). Runs the plain 64-wide single-CTA kernel on the given problem with
+ * every mbarrier wait limited to wait_limit_ns (1 ms .. 100 ms) and with the copy of K block
+ * `skip_kblock` of the first tile left out, so the waits that depend on that block run out.
+ * The kernel returns by itself; device_status (required) then reads
+ * {B200_FP8_MM_DEV_WAIT_EXPIRED, role/barrier, block, phase}, c is not valid, and the context
+ * stays usable. Nothing traps and no wait is unbounded. Arguments a .. ldc as for b200_fp8_mm.
+ */
+int b200_fp8_mm_selftest_wait_expiry(const void* a, const void* b, const float* a_scale, const float* b_scale,
+                                     void* c, int M, int N, int K,
+                                     long long lda, long long ldb,
+                                     long long sa_m, long long sa_k,
+                                     long long sb_n, long long sb_k,
+                                     long long ldc,
+                                     unsigned long long wait_limit_ns, int skip_kblock,
+                                     int* device_status, void* stream);
+
 /* Size in bytes of the scratch array b200_fp8_mm_static_scratch uses. */
 size_t b200_fp8_mm_static_scratch_limit(void);
 
 /* Workspace the plan chosen by b200_fp8_mm / b200_fp8_mm_strided for (M,N,K) needs, in bytes
- * (0 when it does not split K; the larger of the two when the layouts' plans differ). Replaces
+ * (0 when it does not split K; the larger of the two when the layouts' plans differ). The plan
+ * depends on the SM count: the size is for the current CUDA device when there is one (the device
+ * the GEMM will run on must be current), else for B200's 148 SMs. Replaces
  * the reference's per-call `torch.empty(m*n*4)` split-K scratch
  * (1-amd-fp8-mm/amd-fp8-mm-submission.py:597-601). */
 size_t b200_fp8_mm_workspace_bytes(int M, int N, int K);

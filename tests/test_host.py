@@ -108,7 +108,7 @@ def test_selector_is_pure_and_sane(built_library):
         assert p1.block_m == 128 and p1.block_n in (64, 128, 192, 256)
         assert 1 <= p1.split_k <= k // 128
         assert 2 <= p1.stages <= 8 and p1.smem_bytes <= 232448
-        assert p1.store_bufs in (0, 1, 2) and 0 <= p1.full_tiles <= p1.tiles
+        assert p1.store_bufs in (0, 1, 2, 3, 4) and 0 <= p1.full_tiles <= p1.tiles
         assert (p1.full_tiles == p1.tiles) == (p1.split_k == 1)
         assert (p1.store_bufs == 0) == (p1.full_tiles == 0)
         tiles = -(-m // (p1.block_m * (2 if p1.cta_pair else 1))) * -(-n // p1.block_n)

@@ -108,9 +108,9 @@ def test_ragged_and_small_shapes(m, n, k):
 
 
 # every tile width x single CTA / CTA pair x {no split, split-K 3}; without a split also every way
-# the bf16 tile can leave: plain stores (-1), TMA store with 1 or 2 staging buffers
+# the bf16 tile can leave: plain stores (-1), TMA store with 1 or 2 staging buffers (boxes ping-pong) or one per box (4)
 PLANS = [Plan(block_n=bn, cta_pair=pr, split_k=sk, store_bufs=sb)
-         for bn in (64, 128, 192, 256) for pr in (-1, 1) for (sk, sb) in ((1, -1), (1, 1), (1, 2), (3, 0))]
+         for bn in (64, 128, 192, 256) for pr in (-1, 1) for (sk, sb) in ((1, -1), (1, 1), (1, 2), (1, 4), (3, 0))]
 
 
 @pytest.mark.parametrize(

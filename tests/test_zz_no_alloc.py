@@ -96,3 +96,36 @@ def test_a_plan_beyond_the_built_in_scratch_is_refused():
     assert "8 MiB" in _lib.strerror(rc)
     torch.cuda.synchronize()
     assert status.tolist() == [0, 0, 0, 0]
+
+
+def test_a_refused_call_puts_nothing_on_the_stream():
+    """Argument checks come before the clearing of the shared array's counters: a call that is refused
+    (here: an n_phase that is not a multiple of 32) must not enqueue anything. A stream capture serves
+    as the recorder of what reaches the stream; the refused call must leave the captured graph empty."""
+    from cuda.bindings import runtime as rt
+
+    m, n, k = 256, 1536, 7168   # a split-K plan: an accepted call would clear counters first
+    a, b, a_s, b_s, _ = pkg.make_inputs(m, n, k, 44, device="cuda")
+    c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    rc, status = call_static_scratch(a, b, a_s, b_s, c)   # set-up call, outside the recording
+    assert rc == 0 and status[0] == 0
+    lib = _lib.load()
+    status_t = torch.zeros(4, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    (err,) = rt.cudaStreamBeginCapture(stream.cuda_stream, rt.cudaStreamCaptureMode.cudaStreamCaptureModeThreadLocal)
+    assert err == rt.cudaError_t.cudaSuccess
+    try:
+        rc = lib.b200_fp8_mm_static_scratch(
+            a.data_ptr(), b.data_ptr(), a_s.data_ptr(), b_s.data_ptr(), c.data_ptr(), m, n, k,
+            a.stride(0), b.stride(0), a_s.stride(0), a_s.stride(1), b_s.stride(0), b_s.stride(1), c.stride(0), 16,
+            status_t.data_ptr(), stream.cuda_stream)
+    finally:
+        err, graph = rt.cudaStreamEndCapture(stream.cuda_stream)
+    assert err == rt.cudaError_t.cudaSuccess
+    assert rc == 5   # B200_FP8_MM_ERR_PHASE
+    err, _nodes, count = rt.cudaGraphGetNodes(graph, 0)
+    assert err == rt.cudaError_t.cudaSuccess and count == 0
+    rt.cudaGraphDestroy(graph)
+    torch.cuda.synchronize()
+    assert status_t.tolist() == [0, 0, 0, 0]
