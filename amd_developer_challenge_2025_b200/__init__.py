@@ -8,6 +8,7 @@ library is missing the import of ``_lib`` raises.
 """
 from .fp8_mm import Plan, describe, estimate_clocks, fp8_mm, fp8_mm_grouped, fp8_mm_host, workspace_bytes  # noqa: F401
 from .inputs import make_inputs  # noqa: F401
+from .mla import div_softmax, kv_down_projection_fp8, mla_decode  # noqa: F401
 from .sharding import (GridSpec, ShardSpec, choose_grid, gather_c, grid_inputs, grid_spec, shard_inputs,  # noqa: F401
                        shard_spec)
 from .submission import custom_kernel  # noqa: F401

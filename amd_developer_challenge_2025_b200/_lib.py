@@ -1,4 +1,4 @@
-"""ctypes binding of lib/libb200fp8mm.so (declarations: include/b200_fp8_mm.h).
+"""ctypes binding of lib/libb200fp8mm.so (declarations: include/b200_fp8_mm.h, include/b200_mla_consumers.h).
 
 Loading fails loudly: there is no fallback implementation of the operator."""
 from __future__ import annotations
@@ -12,7 +12,7 @@ LIB_PATH = os.environ.get("B200_FP8_MM_LIB") or os.path.join(HERE, "lib", "libb2
 
 ABI_VERSION = 7
 
-# Every symbol include/b200_fp8_mm.h declares.
+# Every symbol the two headers declare.
 EXPORTS = (
     "b200_fp8_mm",
     "b200_fp8_mm_planned",
@@ -27,6 +27,9 @@ EXPORTS = (
     "b200_fp8_mm_estimate_clocks",
     "b200_fp8_mm_strerror",
     "b200_fp8_mm_abi_version",
+    # include/b200_mla_consumers.h
+    "b200_mla_rope",
+    "b200_mla_div_softmax",
 )
 
 
@@ -98,6 +101,11 @@ def load() -> ctypes.CDLL:
     lib.b200_fp8_mm_estimate_clocks.restype = ctypes.c_double
     lib.b200_fp8_mm_strerror.argtypes = [ctypes.c_int]
     lib.b200_fp8_mm_strerror.restype = ctypes.c_char_p
+    lib.b200_mla_rope.argtypes = ([ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 4 + [ctypes.c_longlong] * 4
+                                  + [ctypes.c_void_p])
+    lib.b200_mla_rope.restype = ctypes.c_int
+    lib.b200_mla_div_softmax.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 5 + [ctypes.c_void_p]
+    lib.b200_mla_div_softmax.restype = ctypes.c_int
     lib.b200_fp8_mm_abi_version.argtypes = []
     lib.b200_fp8_mm_abi_version.restype = ctypes.c_int
     if lib.b200_fp8_mm_abi_version() != ABI_VERSION:

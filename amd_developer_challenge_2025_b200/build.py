@@ -10,8 +10,10 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-SRC = os.path.join(HERE, "csrc", "fp8_mm_sm100.cu")
 INCLUDE = os.path.join(ROOT, "include")
+SRC = os.path.join(HERE, "csrc", "fp8_mm_sm100.cu")
+SOURCES = [SRC, os.path.join(HERE, "csrc", "mla_consumers_sm100.cu")]
+HEADERS = [os.path.join(INCLUDE, "b200_fp8_mm.h"), os.path.join(INCLUDE, "b200_mla_consumers.h")]
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libb200fp8mm.so")
 
@@ -24,7 +26,7 @@ def _nvcc() -> str:
 def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
-    newest = max(os.path.getmtime(SRC), os.path.getmtime(os.path.join(INCLUDE, "b200_fp8_mm.h")))
+    newest = max(os.path.getmtime(p) for p in SOURCES + HEADERS)
     return os.path.getmtime(LIB) < newest
 
 
@@ -34,7 +36,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIB_DIR, exist_ok=True)
     cmd = [
         _nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
-        "-I", INCLUDE, "-shared", "-Xcompiler", "-fPIC", "-o", LIB, SRC,
+        "-I", INCLUDE, "-shared", "-Xcompiler", "-fPIC", "-o", LIB, *SOURCES,
     ]
     if verbose:
         cmd.insert(1, "-Xptxas")

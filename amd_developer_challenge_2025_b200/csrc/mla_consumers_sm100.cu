@@ -1,0 +1,142 @@
+// RoPE and scaled softmax for B200 (sm_100a): the two custom kernels around the KV down-projection GEMM in the
+// reference's MLA-decode submission (3-amd-mla-decode/amd-mla-submission.py:17-125 and 127-225). Both are
+// memory-bound elementwise passes over bf16 data; they are written for HBM throughput: 16-byte accesses where
+// the layout allows, enough CTAs to cover every SM several times, no shared-memory staging of the row.
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "b200_fp8_mm.h"
+#include "b200_mla_consumers.h"
+
+namespace {
+
+// bf16 arithmetic as the reference writes it: every operation rounds to bf16 (round to nearest even).
+__device__ __forceinline__ __nv_bfloat16 bf(float v) { return __float2bfloat16_rn(v); }
+__device__ __forceinline__ float fl(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ __nv_bfloat16 bmul(__nv_bfloat16 a, __nv_bfloat16 b) { return bf(fl(a) * fl(b)); }
+__device__ __forceinline__ __nv_bfloat16 badd(__nv_bfloat16 a, __nv_bfloat16 b) { return bf(fl(a) + fl(b)); }
+__device__ __forceinline__ __nv_bfloat16 bsub(__nv_bfloat16 a, __nv_bfloat16 b) { return bf(fl(a) - fl(b)); }
+__device__ __forceinline__ __nv_bfloat16 bdiv(__nv_bfloat16 a, __nv_bfloat16 b) { return bf(__fdiv_rn(fl(a), fl(b))); }
+
+// The rotation's (cos, sin) for position row i1 and pair index j: a function of (i1, j) only
+// (3-amd-mla-decode/amd-mla-submission.py:21-31).
+__device__ __forceinline__ void rope_angle(int pos, int i1, int j, int d2, __nv_bfloat16* c, __nv_bfloat16* s) {
+  const __nv_bfloat16 idx = badd(bf(static_cast<float>(pos)), bf(static_cast<float>(i1)));
+  __nv_bfloat16 theta = bf(static_cast<float>(j));
+  theta = bmul(theta, bf(-2.0f));
+  theta = bdiv(theta, bf(static_cast<float>(d2)));
+  theta = bf(powf(fl(bf(10000.0f)), fl(theta)));
+  theta = bmul(theta, idx);
+  *c = bf(cosf(fl(theta)));
+  *s = bf(sinf(fl(theta)));
+}
+
+// One thread owns one (i1, j) pair and a share of the d0 rows: the angle is computed once and reused for
+// every row. Consecutive threads take consecutive j, so a warp reads two runs of 64 contiguous bytes per row.
+// grid.x covers the d1 * d2/2 pairs, grid.y cuts d0 so that small d1 (the query: one position) still fills the GPU.
+__global__ void __launch_bounds__(256) rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* y, int pos,
+                                                   int d0, int d1, int d2, long long xs1, long long xs2,
+                                                   long long ys1, long long ys2, int rows_per_block) {
+  const int half = d2 >> 1;
+  const long long pair = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (pair >= static_cast<long long>(d1) * half) return;
+  const int i1 = static_cast<int>(pair / half);
+  const int j = static_cast<int>(pair - static_cast<long long>(i1) * half);
+  __nv_bfloat16 c, s;
+  rope_angle(pos, i1, j, d2, &c, &s);
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(d0, r0 + rows_per_block);
+  const __nv_bfloat16* xp = x + static_cast<long long>(i1) * xs2 + j;
+  __nv_bfloat16* yp = y + static_cast<long long>(i1) * ys2 + j;
+  for (int i0 = r0; i0 < r1; ++i0) {
+    const __nv_bfloat16 x1 = xp[i0 * xs1];
+    const __nv_bfloat16 x2 = xp[i0 * xs1 + half];
+    yp[i0 * ys1] = bsub(bmul(x1, c), bmul(x2, s));
+    yp[i0 * ys1 + half] = badd(bmul(x2, c), bmul(x1, s));
+  }
+}
+
+constexpr int kSoftmaxThreads = 512;
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < kSoftmaxThreads / 32) ? scratch[lane] : 0.f;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+
+// One CTA per row. Pass 1 reads the row (16-byte loads where the row is 16-byte aligned), forms e = expf(v * scale)
+// and the fp32 row sum; pass 2 reads the row again (it is in L1/L2 now), rounds e to bf16 as the reference keeps
+// it, divides by the sum and writes in place. HBM sees one read and one write of the row.
+__global__ void __launch_bounds__(kSoftmaxThreads) div_softmax_kernel(__nv_bfloat16* qk, int sl, float scale) {
+  __shared__ float scratch[kSoftmaxThreads / 32];
+  __nv_bfloat16* row = qk + static_cast<long long>(blockIdx.x) * sl;
+  const bool vec = (reinterpret_cast<uintptr_t>(row) % 16) == 0;
+  const int sl_vec = vec ? (sl / 8) * 8 : 0;
+  float sum = 0.f;
+  for (int i = threadIdx.x * 8; i < sl_vec; i += kSoftmaxThreads * 8) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sum += expf(fl(v[e]) * scale);
+  }
+  for (int i = sl_vec + threadIdx.x; i < sl; i += kSoftmaxThreads) sum += expf(fl(row[i]) * scale);
+  const float total = block_sum(sum, scratch);
+  for (int i = threadIdx.x * 8; i < sl_vec; i += kSoftmaxThreads * 8) {
+    uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+    __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = bf(__fdiv_rn(fl(bf(expf(fl(v[e]) * scale))), total));
+    *reinterpret_cast<uint4*>(row + i) = raw;
+  }
+  for (int i = sl_vec + threadIdx.x; i < sl; i += kSoftmaxThreads)
+    row[i] = bf(__fdiv_rn(fl(bf(expf(fl(row[i]) * scale))), total));
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_mla_rope(const void* x, void* y, int pos, int d0, int d1, int d2, long long xs1, long long xs2,
+                  long long ys1, long long ys2, void* stream) {
+  if (x == nullptr || y == nullptr) return B200_FP8_MM_ERR_NULL;
+  if (d0 <= 0 || d1 <= 0 || d2 <= 0 || (d2 & 1) != 0) return B200_FP8_MM_ERR_SHAPE;
+  const long long pairs = static_cast<long long>(d1) * (d2 / 2);
+  const int threads = 256;
+  const long long blocks_x = (pairs + threads - 1) / threads;
+  if (blocks_x > 0x7fffffffll) return B200_FP8_MM_ERR_SHAPE;
+  // enough CTAs for every SM a few times over, without cutting d0 finer than 4 rows per CTA
+  long long want_y = (148 * 8 + blocks_x - 1) / blocks_x;
+  if (want_y > (d0 + 3) / 4) want_y = (d0 + 3) / 4;
+  if (want_y < 1) want_y = 1;
+  if (want_y > 65535) want_y = 65535;
+  const int rows_per_block = static_cast<int>((d0 + want_y - 1) / want_y);
+  const int blocks_y = (d0 + rows_per_block - 1) / rows_per_block;
+  rope_kernel<<<dim3(static_cast<unsigned>(blocks_x), static_cast<unsigned>(blocks_y)), threads, 0,
+                static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
+                                                     static_cast<__nv_bfloat16*>(y), pos, d0, d1, d2, xs1, xs2, ys1,
+                                                     ys2, rows_per_block);
+  if (cudaGetLastError() != cudaSuccess) return B200_FP8_MM_ERR_LAUNCH;
+  return B200_FP8_MM_OK;
+}
+
+int b200_mla_div_softmax(void* qk, int bs, int nh, int sl, int dnope, int drope, void* stream) {
+  if (qk == nullptr) return B200_FP8_MM_ERR_NULL;
+  if (bs <= 0 || nh <= 0 || sl <= 0 || dnope + drope <= 0) return B200_FP8_MM_ERR_SHAPE;
+  const long long rows = static_cast<long long>(bs) * nh;
+  if (rows > 0x7fffffffll) return B200_FP8_MM_ERR_SHAPE;
+  const float scale = 1.0f / sqrtf(static_cast<float>(dnope + drope));
+  div_softmax_kernel<<<static_cast<unsigned>(rows), kSoftmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(qk), sl, scale);
+  if (cudaGetLastError() != cudaSuccess) return B200_FP8_MM_ERR_LAUNCH;
+  return B200_FP8_MM_OK;
+}
+
+}  // extern "C"

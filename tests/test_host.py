@@ -12,9 +12,14 @@ HEADER = os.path.join(ROOT, "include", "b200_fp8_mm.h")
 
 
 def header_functions():
-    text = open(HEADER).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(b200_fp8_mm\w*)\s*\(", text)))
+    """Every function any header under include/ declares."""
+    names = set()
+    inc = os.path.dirname(HEADER)
+    for f in sorted(os.listdir(inc)):
+        if f.endswith(".h"):
+            text = re.sub(r"/\*.*?\*/", "", open(os.path.join(inc, f)).read(), flags=re.S)
+            names |= set(re.findall(r"\b(b200_(?:fp8_mm|mla)\w*)\s*\(", text))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol(built_library):
