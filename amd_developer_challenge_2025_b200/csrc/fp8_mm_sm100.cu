@@ -504,22 +504,17 @@ struct TileCfg {
   // Register split after setmaxnreg (light: producer / MMA / loader warps, heavy: promotion warps):
   // 128 * light + kEpiThreads * heavy is at most the allocation the CTA is launched with
   // (384 threads x 168 registers).
-#ifndef FP8MM_X_REGS_LIGHT
-#define FP8MM_X_REGS_LIGHT 104
-#define FP8MM_X_REGS_HEAVY 200
-#endif
-#ifndef FP8MM_X_CC256
-#define FP8MM_X_CC256 32
-#endif
-#ifndef FP8MM_X_PACKED256
-#define FP8MM_X_PACKED256 64
-#endif
-  static constexpr int kRegsLight = BN == 256 ? FP8MM_X_REGS_LIGHT : 104;
-  static constexpr int kRegsHeavy = BN == 256 ? FP8MM_X_REGS_HEAVY : 200;
+  // The 256-wide pair tile trades registers of the light warps for a 64-register landing area in the promotion
+  // warps (128 accumulators + 64 + addressing): two 64-column fetches per K block instead of four 32-column
+  // ones measured 1.7 % faster on the headline GEMM. The single-CTA 256-wide kernel keeps the old split: its
+  // light warps spill at 56 registers and it ran 40 % slower.
+  static constexpr bool kWideLanding = (BN == 256) && PAIR;
+  static constexpr int kRegsLight = kWideLanding ? 56 : 104;
+  static constexpr int kRegsHeavy = kWideLanding ? 224 : 200;
   // Columns fetched from TMEM per tcgen05.ld: as wide as the registers allow without spilling
   // next to the accumulators. tcgen05.wait::ld waits for every outstanding fetch; keeping two
   // 32-column fetches in flight with two landing areas was measured 5-8 % slower than one at a time.
-  static constexpr int kChunkCols = (kColsPerThread == 64) ? 64 : (BN == 256 ? FP8MM_X_CC256 : 32);
+  static constexpr int kChunkCols = (kColsPerThread == 64 || kWideLanding) ? 64 : 32;
   static constexpr int kChunks = kColsPerThread / kChunkCols;
   // Accumulators as packed pairs (fma.rn.f32x2: half the issue slots) or as scalars. With 128 columns per
   // thread the packed form spills (the pairs want aligned 64-bit registers next to a 32-register landing
@@ -527,20 +522,13 @@ struct TileCfg {
   static constexpr bool kScalarAcc = (BN == 256);
   // At BN=256 the first 64 of a thread's 128 columns stay packed (no spill, 1 % faster than all scalar);
   // 96 packed columns spill again.
-  static constexpr int kPackedCols = kScalarAcc ? FP8MM_X_PACKED256 : kColsPerThread;
+  static constexpr int kPackedCols = kScalarAcc ? 64 : kColsPerThread;
   // Narrow tiles: the promotion warps probe the next K block's barrier (non-blocking) right after they
   // release a buffer, so the answer arrives during the fmas and the blocking wait is skipped when the
   // block is already there. Measured -3 % at 64 and 128 columns, 0 at 256, +2.6 % on 192-wide pairs.
   static constexpr bool kEarlyProbe = (BN <= 128);
-#ifndef FP8MM_X_HALF
-#define FP8MM_X_HALF 0
-#endif
-  // 256-wide pair tiles: a K block is issued as two groups of N=128 instructions (columns 0-127, then
-  // 128-255), each with its own commit, and each promotion warpgroup waits for, drains and hands back
-  // only its own half of the TMEM buffer: four half buffers cycling independently instead of two whole
-  // ones. For that each CTA's share of the B tile is rows {0-63, 128-191} + 64 * rank of the tile (two
-  // TMA boxes), so that an N=128 instruction reading 64 rows from each CTA covers 128 adjacent columns.
-  static constexpr bool kHalf = PAIR && BN == 256 && (FP8MM_X_HALF != 0);
+
+
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "block_n must be 64, 128, 192 or 256");
 };
 
@@ -617,13 +605,11 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   uint8_t* ring = smem + kHeaderBytes;
   uint64_t* full_bar = bars;                                 // [kMaxStages]
   uint64_t* done_bar = bars + kMaxStages;                    // [kMaxStages]
-  uint64_t* done_lo_bar = bars + 2 * kMaxStages;             // [kMaxStages], kHalf: commit of columns 0-127
   uint64_t* scale_full_bar = bars + 2 * kMaxStages + 8;      // [kScaleSlots]
   uint64_t* scale_empty_bar = scale_full_bar + kScaleSlots;  // [kScaleSlots]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(scale_empty_bar + kScaleSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 2);
-  uint64_t* hi_free_bar = bars + 40;                         // [kMaxStages], kHalf: columns 128-255 drained
   // staging for the TMA store of c: [warpgroup][buffer][128 rows x 64 B], behind the ring (1024-byte aligned:
   // the header and every stage are multiples of 1024 bytes)
   uint8_t* staging = ring + stages * Cfg::kStageBytes;
@@ -636,16 +622,8 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
       // one arrive.expect_tx per producing CTA + one release per promotion warp (of both CTAs)
-#ifdef FP8MM_X_FREERUN
-      mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1));
-#else
-      mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1) * (1 + (Cfg::kHalf ? Cfg::kEpiWarps / 2 : Cfg::kEpiWarps)));
-#endif
+      mbar_init(smem_u32(&full_bar[s]), (PAIR ? 2 : 1) * (1 + Cfg::kEpiWarps));
       mbar_init(smem_u32(&done_bar[s]), 1);  // the MMA thread's commit
-      if constexpr (Cfg::kHalf) {
-        mbar_init(smem_u32(&done_lo_bar[s]), 1);
-        mbar_init(smem_u32(&hi_free_bar[s]), 2 * (Cfg::kEpiWarps / 2));
-      }
     }
     for (int s = 0; s < kScaleSlots; ++s) {
       mbar_init(smem_u32(&scale_full_bar[s]), 32);
@@ -702,7 +680,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           const WorkItem it = decode_work<GENERIC>(p, w, Cfg::kTileM, BN);
           if (it.skip) continue;
           const int a_row = it.m0 + static_cast<int>(cta_rank) * kBlockM;
-          const int b_row = it.n0 + static_cast<int>(cta_rank) * (PAIR ? (Cfg::kHalf ? 64 : Cfg::kRowsB) : 0);
+          const int b_row = it.n0 + static_cast<int>(cta_rank) * (PAIR ? Cfg::kRowsB : 0);
           for (int kb = it.kb_begin; kb < it.kb_end; ++kb) {
             if (!mbar_wait(smem_u32(&done_bar[stage]), phase ^ 1u, ctx, 0x100 | stage)) {
               ok = false;
@@ -732,22 +710,14 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             // K-major: x = byte of K, y = matrix row. MN-major: x = matrix row (a multiple of 64), y = k.
             if (GENERIC && p.groups > 0) {
               tma_load_3d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, it.group, fb);
-              if constexpr (Cfg::kHalf) {
-                tma_load_3d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
-                tma_load_3d<PAIR>(sa + Cfg::kStageBytesA + 64 * kBlockK, &tmap_b, kb * kBlockK, b_row + 128, it.group, fb);
-              } else {
-                tma_load_3d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
-              }
+              tma_load_3d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, it.group, fb);
             } else {
             if (!GENERIC || !p.a_mn) {
               tma_load_2d<PAIR>(sa, &tmap_a, kb * kBlockK, a_row, fb);
             } else {
               tma_load_2d<PAIR>(sa, &tmap_a, a_row, kb * kBlockK, fb);
             }
-            if constexpr (Cfg::kHalf) {
-              tma_load_2d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, fb);
-              tma_load_2d<PAIR>(sa + Cfg::kStageBytesA + 64 * kBlockK, &tmap_b, kb * kBlockK, b_row + 128, fb);
-            } else if (!GENERIC || !p.b_mn) {
+            if (!GENERIC || !p.b_mn) {
               tma_load_2d<PAIR>(sa + Cfg::kStageBytesA, &tmap_b, kb * kBlockK, b_row, fb);
             } else {
               for (int i = 0; i < p.b_boxes; ++i)
@@ -777,7 +747,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
       // thread roughly 100 clocks), more than the tensor pipe needs for a narrow tile's block.
       if (lane == 0 && cta_rank == 0 && warp - 1 < p.issuers) {
         constexpr uint32_t kHiK = (1024u >> 4) | (1u << 14) | (2u << 29);  // K-major, 128-byte swizzle
-        const uint32_t idesc = make_idesc(Cfg::kTileM, Cfg::kHalf ? BN / 2 : BN) | (GENERIC ? p.idesc_major : 0u);
+        const uint32_t idesc = make_idesc(Cfg::kTileM, BN) | (GENERIC ? p.idesc_major : 0u);
         const uint32_t a_hi = GENERIC ? p.a_desc_hi : kHiK, b_hi = GENERIC ? p.b_desc_hi : kHiK;
         const uint32_t a_kstep = GENERIC ? p.a_kstep : 2u, b_kstep = GENERIC ? p.b_kstep : 2u;
         const uint32_t a_lo_bits = GENERIC ? p.a_desc_lo : (1u << 16), b_lo_bits = GENERIC ? p.b_desc_lo : (1u << 16);
@@ -814,20 +784,6 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
               umma_f8<PAIR>(d_addr, a_lo + a_kstep * k, b_lo + b_kstep * k, a_hi, b_hi, idesc, k > 0 ? 1u : 0u);
             }
 #endif
-            if constexpr (Cfg::kHalf) {
-              umma_commit<PAIR>(smem_u32(&done_lo_bar[my_stage]));
-              // columns 128-255: the same A, the second 64 rows of each CTA's share of B
-              if (!mbar_wait(smem_u32(&hi_free_bar[my_stage]), my_phase, ctx, 0x700 | my_stage)) {
-                ok = false;
-                break;
-              }
-              tcgen05_fence_after();
-#pragma unroll
-              for (int k = 0; k < kMmasPerBlock; ++k) {
-                umma_f8<PAIR>(d_addr + BN / 2, a_lo + a_kstep * k, b_lo + ((64u * kBlockK) >> 4) + b_kstep * k, a_hi, b_hi,
-                              idesc, k > 0 ? 1u : 0u);
-              }
-            }
             umma_commit<PAIR>(smem_u32(&done_bar[my_stage]));
             my_stage += step;
             if (my_stage >= stages) {
@@ -906,14 +862,9 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     // "Buffer drained" is reported to the full barrier of the stage whose K block will overwrite the
     // buffer: kTmemBufs K blocks after the one just read. The MMA thread that waits on it lives in
     // the leader CTA.
-    // kHalf: the warpgroup of columns 128-255 reports to the issuer's second barrier of the stage
-    const uint32_t rel_local = (Cfg::kHalf && half == 1) ? smem_u32(&hi_free_bar[0]) : smem_u32(&full_bar[0]);
-    const uint32_t full_base = PAIR ? map_to_cta(rel_local, 0) : rel_local;
-    const uint32_t ready_base = (Cfg::kHalf && half == 0) ? smem_u32(&done_lo_bar[0]) : smem_u32(&done_bar[0]);
+    const uint32_t full_base = PAIR ? map_to_cta(smem_u32(&full_bar[0]), 0) : smem_u32(&full_bar[0]);
+    const uint32_t ready_base = smem_u32(&done_bar[0]);
     auto release_to = [&](int st) {
-#ifdef FP8MM_X_FREERUN
-      return;
-#endif
       if (lane == 0) {
         if constexpr (PAIR) {
           mbar_arrive_cluster(full_base + static_cast<uint32_t>(st * 8));
@@ -921,6 +872,12 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           mbar_arrive(full_base + static_cast<uint32_t>(st * 8));
         }
       }
+    };
+    // A wait of the whole warp, with the same outcome in every lane (the warp-wide TMEM fetches need all 32).
+    // (Every lane probes the barrier itself: one lane probing for the warp and broadcasting its answer measured
+    // 5 % slower, and one arrival per warpgroup behind a named barrier instead of one per warp 2 % slower.)
+    auto warp_wait = [&](uint32_t bar, uint32_t parity, int where) -> bool {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, where));
     };
     // Nothing was read before the first kTmemBufs K blocks: their buffers start out drained.
     for (int b = 0; b < nbufs; ++b) release_to(b);
@@ -957,7 +914,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         // Scales of the next (up to) four K blocks: three 16-byte shared-memory loads, then the
         // slot goes back to the loader.
         // (the vote makes the outcome the same in every lane: the warp-wide TMEM fetches below need all 32)
-        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&scale_full_bar[slot]), sphase, ctx, 0x600 | slot))) {
+        if (!warp_wait(smem_u32(&scale_full_bar[slot]), sphase, 0x600 | slot)) {
           ok = false;
           break;
         }
@@ -978,8 +935,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         for (int u = 0; u < kScaleGroup; ++u) {
           if (kb0 + u >= it.kb_end) break;
           if (!(Cfg::kEarlyProbe && ready_next)) {
-            if (!__all_sync(0xffffffffu,
-                            mbar_wait(ready_base + static_cast<uint32_t>(cstage * 8), cphase, ctx, 0x400 | cstage))) {
+            if (!warp_wait(ready_base + static_cast<uint32_t>(cstage * 8), cphase, 0x400 | cstage)) {
               ok = false;
               break;
             }
@@ -1393,12 +1349,8 @@ bool encode_output_map_3d(CUtensorMap* map, void* base, int groups, int M, int N
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-// Rows of b per TMA box of one CTA (K-major b). A pair's 256-wide tile takes its share of b as two boxes of
-// 64 rows (see TileCfg::kHalf).
-int b_box_rows_for(int block_n, int pair) {
-  if (!pair) return block_n;
-  return (block_n == 256 && FP8MM_X_HALF != 0) ? 64 : block_n / 2;
-}
+// Rows of b per TMA box of one CTA (K-major b): a CTA of a pair loads half of the tile's rows.
+int b_box_rows_for(int block_n, int pair) { return pair ? block_n / 2 : block_n; }
 
 int epi_warps_for(int block_n) {
   (void)block_n;
@@ -1433,22 +1385,22 @@ int max_stages_for(int block_n, int pair, int store_bufs) {
   return s;
 }
 
-// Staging buffers per warpgroup for the TMA store of c. Short K (a tile is only a few K blocks long, so the
-// epilogue is a large share of it and the ring need not be deep): one buffer for every 32-column box of the
-// warpgroup's share, so that the whole tile is staged at once and its stores drain under the next tile.
-// Otherwise two (the store of one box overlaps the staging of the next) unless that would leave fewer than
-// four ring stages.
+// Staging buffers per warpgroup for the TMA store of c. Where the ring keeps four stages (or as many as a
+// tile has K blocks) beside it: one buffer for every 32-column box of the warpgroup's share, so that the whole
+// tile is staged between two barriers and its stores drain under the next tile. Otherwise two (the store of
+// one box overlaps the staging of the next) unless that too would leave fewer than four ring stages.
 int store_boxes_per_group(int block_n) { return block_n / (epi_warps_for(block_n) / 4) / kStoreBoxCols; }
 
 int store_bufs_for(int block_n, int pair, int kblocks_per_item) {
-  if (kblocks_per_item <= 8) {
-    const int all = store_boxes_per_group(block_n);
-    if (max_stages_for(block_n, pair, all) >= (kblocks_per_item < 4 ? kblocks_per_item : 4)) return all;
-    return 2 < all ? 2 : all;
-  }
+  const int all = store_boxes_per_group(block_n);
+  const int two = 2 < all ? 2 : all;
+  const int need = kblocks_per_item < 4 ? kblocks_per_item : 4;
+  if (max_stages_for(block_n, pair, all) >= need || max_stages_for(block_n, pair, all) == max_stages_for(block_n, pair, two))
+    return all;
+  if (kblocks_per_item <= 8) return two;
   // measured: a second staging buffer is worth more than a fifth (single CTA) or seventh (pair) ring stage
   const int with_two = max_stages_for(block_n, pair, 2);
-  return (with_two >= 4 || with_two == max_stages_for(block_n, pair, 1)) ? 2 : 1;
+  return (with_two >= 4 || with_two == max_stages_for(block_n, pair, 1)) ? two : 1;
 }
 
 bool valid_block_n(int bn) { return bn == 64 || bn == 128 || bn == 192 || bn == 256; }
@@ -1592,7 +1544,7 @@ bool plan_is_supported(const b200_fp8_mm_plan& pl, int kblocks) {
 
 typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const KernelParams);
 
-// generic: MN-major operands or a grouped launch (single CTAs only).
+// generic: MN-major operands or a grouped launch (CTA pairs at the 192- and 256-wide tiles only).
 KernelFn kernel_for(int block_n, int pair, bool generic) {
   if (generic) {
     if (pair) {
@@ -1686,10 +1638,20 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
   const int sm_count = device_sm_count();
   if (sm_count <= 0) return B200_FP8_MM_ERR_DRIVER;
 
-  // CTA pairs exist for K-major operands only.
-  b200_fp8_mm_plan forced_copy;
+  // MN-major operands run the GENERIC kernels, which exist for CTA pairs at the 192- and 256-wide tiles. An
+  // MN-major b needs the CTA's half of the tile's columns to be whole 64-byte boxes, i.e. the 256-wide pair
+  // (128 columns per CTA). Where the chosen pair plan has no such kernel, single CTAs are planned instead.
+  const bool generic = a_mn || b_mn;
+  auto pair_plan_runs = [&](const b200_fp8_mm_plan& q) {
+    if (!generic || !q.cta_pair) return true;
+    if (kernel_for(q.block_n, 1, true) == nullptr) return false;
+    return !b_mn || ((q.block_n / 2) % 64) == 0;
+  };
   const b200_fp8_mm_plan* forced = forced_in;
-  if (a_mn || b_mn) {
+  b200_fp8_mm_plan pl;
+  choose_plan(M, N, K, sm_count, forced, &pl);
+  b200_fp8_mm_plan forced_copy;
+  if (!pair_plan_runs(pl)) {
     if (forced_in != nullptr && forced_in->cta_pair > 0) return B200_FP8_MM_ERR_PLAN;
     if (forced_in != nullptr) {
       forced_copy = *forced_in;
@@ -1698,9 +1660,8 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
     }
     forced_copy.cta_pair = -1;
     forced = &forced_copy;
+    choose_plan(M, N, K, sm_count, forced, &pl);
   }
-  b200_fp8_mm_plan pl;
-  choose_plan(M, N, K, sm_count, forced, &pl);
   const int kblocks = K / kBlockK;
   if (!plan_is_supported(pl, kblocks)) return B200_FP8_MM_ERR_PLAN;
   const size_t need = plan_workspace_bytes(pl);
@@ -1708,7 +1669,7 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
                    (reinterpret_cast<uintptr_t>(workspace) % 256) != 0))
     return B200_FP8_MM_ERR_WORKSPACE;
 
-  KernelFn fn = kernel_for(pl.block_n, pl.cta_pair, a_mn || b_mn);
+  KernelFn fn = kernel_for(pl.block_n, pl.cta_pair, generic);
   if (fn == nullptr) return B200_FP8_MM_ERR_PLAN;
 
   CUtensorMap map_a, map_b, map_c;

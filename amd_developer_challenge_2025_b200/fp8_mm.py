@@ -5,7 +5,7 @@ Mirrors the reference's pybind launcher `fp8_mm(a, b, as, bs, c, c_tmp)`
 from __future__ import annotations
 
 import ctypes
-from dataclasses import dataclass, replace
+from dataclasses import dataclass
 
 import torch
 
@@ -147,9 +147,6 @@ def _validate(a, b, a_scale, b_scale, c, n_phase, plan):
     _check(c.stride(1) == 1, "c must have N contiguous")
     dev = a.device
     _check(all(t.device == dev for t in (b, a_scale, b_scale, c)), "tensors on different devices")
-    if plan is not None and mn_major:
-        _check(plan.cta_pair <= 0, "CTA pairs need K-major a and b")
-        plan = replace(plan, cta_pair=-1)  # the plan the library sizes the workspace for
     return workspace_bytes(m, n, k, plan), (plan.to_c() if plan is not None else None)
 
 

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import amd_developer_challenge_2025_b200 as pkg
-from amd_developer_challenge_2025_b200.fp8_mm import Plan, check_device_status
+from amd_developer_challenge_2025_b200.fp8_mm import Fp8MmError, Plan, check_device_status
 from amd_developer_challenge_2025_b200.inputs import mn_major
 from oracle import fp8_mm_oracle as oracle
 
@@ -75,22 +75,47 @@ def test_ragged_shapes(m, n, k):
 
 
 def test_headline_equals_k_major_bits_under_the_same_plan():
-    """Same plan, same products, same order: the MN-major run reproduces the K-major bits. (The automatic plans
-    differ - CTA pairs exist for K-major operands only - so the automatic MN-major run is checked against the
-    oracle on sampled rows instead.)"""
+    """Same plan, same products, same order: the MN-major run reproduces the K-major bits, for the single-CTA
+    plan and for the 256-wide CTA-pair plan (the automatic choice for this shape in either storage)."""
     m, n, k = 8192, 4608, 7168
     a, b, a_s, b_s, c = pkg.make_inputs(m, n, k, 65436, device="cuda")
     am, bm = mn_major(a), mn_major(b)
-    plan = Plan(block_n=192, cta_pair=-1, split_k=1)
-    run(a, b, a_s, b_s, c, plan=plan)
-    c2 = torch.full_like(c, float("nan"))
-    run(am, bm, a_s, b_s, c2, plan=plan)
-    assert torch.equal(c2.view(torch.int16), c.view(torch.int16))
-    c2.fill_(float("nan"))
-    run(am, bm, a_s, b_s, c2)
+    assert pkg.describe(m, n, k).cta_pair == 1 and pkg.describe(m, n, k).block_n == 256
+    for plan in (Plan(block_n=192, cta_pair=-1, split_k=1), Plan(block_n=256, cta_pair=1, split_k=1), None):
+        run(a, b, a_s, b_s, c, plan=plan)
+        c2 = torch.full_like(c, float("nan"))
+        run(am, bm, a_s, b_s, c2, plan=plan)
+        assert torch.equal(c2.view(torch.int16), c.view(torch.int16)), str(plan)
     rows = torch.tensor([0, 127, 128, 4095, 4096, 8191], device="cuda")
     assert_close(c2[rows], oracle.dequant_matmul(a[rows], b, a_s[rows], b_s), "automatic MN-major plan")
     assert torch.isfinite(c2.float()).all()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", LAYOUTS, ids=["a_mn", "b_mn", "both_mn"])
+@pytest.mark.parametrize("bn", [192, 256])
+def test_cta_pairs_with_mn_major_operands(bn, a_mn, b_mn):
+    """CTA pairs take MN-major operands where a paired kernel exists: any a at the 192- and 256-wide tiles, an
+    MN-major b at the 256-wide tile only (each CTA's half of the columns must be whole 64-byte boxes). A forced
+    pair plan outside that set is refused; the automatic plan falls back to single CTAs."""
+    from amd_developer_challenge_2025_b200.fp8_mm import Fp8MmError
+
+    m, n, k = 1100, 1104, 1024
+    a, b, a_s, b_s, c = pkg.make_inputs(m, n, k, 98, device="cuda")
+    ref = oracle.dequant_matmul(a, b, a_s, b_s)
+    aa = mn_major(a) if a_mn else a
+    bb = mn_major(b) if b_mn else b
+    plan = Plan(block_n=bn, cta_pair=1, split_k=1)
+    if b_mn and bn == 192:
+        with pytest.raises(Fp8MmError):
+            pkg.fp8_mm(aa, bb, a_s, b_s, c, plan=plan)
+        check_device_status()
+        return
+    want = torch.empty_like(c)
+    run(a, b, a_s, b_s, want, plan=plan)
+    c.fill_(float("nan"))
+    run(aa, bb, a_s, b_s, c, plan=plan)
+    assert_close(c, ref, f"pair bn={bn}")
+    assert torch.equal(c.view(torch.int16), want.view(torch.int16))
 
 
 @pytest.mark.parametrize("world", [2, 8])
@@ -111,8 +136,8 @@ def test_column_shards_of_an_mn_major_b_are_views(world):
 
 def test_layout_errors():
     a, b, a_s, b_s, c = pkg.make_inputs(128, 128, 256, 1, device="cuda", layout="mn")
-    with pytest.raises(ValueError):
-        pkg.fp8_mm(a, b, a_s, b_s, c, plan=Plan(cta_pair=1))           # pairs are K-major only
+    with pytest.raises(Fp8MmError):
+        pkg.fp8_mm(a, b, a_s, b_s, c, plan=Plan(block_n=128, cta_pair=1))   # no paired kernel at this width
     with pytest.raises(ValueError):
         pkg.fp8_mm(a[::2], b, a_s[::2], b_s, c[::2])                   # neither dimension contiguous
     a24, b24, as24, bs24, c24 = pkg.make_inputs(24, 128, 128, 2, device="cuda", layout="mn")
