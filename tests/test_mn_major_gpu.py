@@ -99,7 +99,7 @@ def test_cta_pairs_with_mn_major_operands(bn, a_mn, b_mn):
     pair plan outside that set is refused; the automatic plan falls back to single CTAs."""
     from amd_developer_challenge_2025_b200.fp8_mm import Fp8MmError
 
-    m, n, k = 1100, 1104, 1024
+    m, n, k = 1104, 1104, 1024   # MN-major storage needs M and N to be multiples of 16 (the pitch)
     a, b, a_s, b_s, c = pkg.make_inputs(m, n, k, 98, device="cuda")
     ref = oracle.dequant_matmul(a, b, a_s, b_s)
     aa = mn_major(a) if a_mn else a
