@@ -358,6 +358,7 @@ def sweep_shapes(pkg, ranks, rank, dev, peaks, fp8_peak):
             outs.append(torch.empty(ml, nl, dtype=torch.bfloat16, device=dev))
             del a, b, a_s, b_s
         graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())  # the inputs were generated on the current stream
         with torch.cuda.stream(side):
             # first call on this stream outside the capture: the wrapper's per-stream workspace is made here
             pkg.fp8_mm(*ins[0], outs[0], n_phase=spec.n_phase)
@@ -504,7 +505,9 @@ def run_ours(args):
     e2e_steps = max(3, min(args.steps, 20))
     for _ in range(3):
         pkg.fp8_mm_host(ha, hb, has_, hbs, hc, device=dev, n_phase=spec.n_phase)
-    e2e_ok = ranks.all_true(bool(torch.equal(hc.view(torch.int16), sets[0][4].cpu().view(torch.int16))))
+    # the host path runs the rows in ranges, each with the plan of its own size: same arithmetic per element, but a
+    # range whose plan splits K adds its K ranges in another order, so the check is the tolerance, not the bits
+    e2e_ok = ranks.all_true(spot_check(*sets[0][:4], hc.to(dev), n_phase=spec.n_phase))
     ranks.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -565,7 +568,7 @@ def run_ours(args):
                           "value": round(flops / (sus_ms * 1e-3) / 1e12, 2), "unit": UNIT,
                           "note": "the same launches back to back for at least one second (power cap settled)"},
             "e2e": {"value": round(flops / (e2e_ms * 1e-3) / 1e12, 3), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "bit_equal_to_device_path": e2e_ok},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "spot_check_pass": e2e_ok},
             "gpu_launches": args.steps,
             "clocks": clocks,
         }
