@@ -7,10 +7,10 @@ scales, bf16 out). With N GPUs (one process per GPU under torch.distributed.run)
 fixed (strong scaling) and c stays sharded; there is no data-path collective. Two partitions are timed
 in the same run:
 
-* `value`: the configuration's stated one, b / b_scale cut along N only (576 columns per GPU at 8; odd
-  ranks start 64 columns into a scale block), a / a_scale replicated;
-* `row_column_grid`: the grid of row x column blocks the library's cost model rates fastest
-  (4 x 2 at 8 GPUs), reported beside it.
+* `value`: the grid of row x column blocks of c that the library's cost model rates fastest (1 x 2, 2 x 2 and
+  4 x 2 at 2, 4 and 8 GPUs: b / b_scale cut along N, and a / a_scale along M where that fills the SMs better);
+* `column_only`: the cut the configuration states, b / b_scale along N only (576 columns per GPU at 8; odd
+  ranks start 64 columns into a scale block), a / a_scale replicated, reported beside it in the same line.
 
 Rank 0 prints ONE JSON line. `--impl reference` times the reference's own path for this operator on
 the host cores: its two dequantise kernels (compiled for the host from the reference's text when that
@@ -412,7 +412,7 @@ def run_ours(args):
     if sampler:
         sampler.start()  # runs from before the warm-up to the end of the sustained loop
 
-    main_run = time_partition(pkg, ranks, m_full, n, k, stated, rank, args.steps, args.warmup, dev)
+    main_run = time_partition(pkg, ranks, m_full, n, k, chosen, rank, args.steps, args.warmup, dev)
     spec, sets, ms, ms_local = main_run["spec"], main_run["sets"], main_run["ms"], main_run["ms_local"]
     m, n_loc = spec.m_local, spec.n_local
 
@@ -434,15 +434,18 @@ def run_ours(args):
             clocks = sampler.summary(ts0, ts1, f"the sustained loop of {sus_steps} steps that follows the timed steps "
                                                f"(the timed region is shorter than three 10 ms samples)")
 
-    grid_run = None
+    column_only = None
     if world > 1 and chosen != stated:
         del main_run["fns"]
-        g = time_partition(pkg, ranks, m_full, n, k, chosen, rank, args.steps, args.warmup, dev)
-        grid_run = {"grid": f"{chosen[0]}x{chosen[1]}", "ms_per_step": round(g["ms"], 5),
-                    "value": round(2.0 * m_full * n * k / (g["ms"] * 1e-3) / 1e12, 2), "unit": UNIT,
-                    "block": f"{g['spec'].m_local} rows x {g['spec'].n_local} columns per GPU",
-                    "plan": plan_text(g["plan"]), "spot_check_pass": g["ok"]}
+        g = time_partition(pkg, ranks, m_full, n, k, stated, rank, args.steps, args.warmup, dev)
+        column_only = {"grid": f"{stated[0]}x{stated[1]}", "ms_per_step": round(g["ms"], 5),
+                       "value": round(2.0 * m_full * n * k / (g["ms"] * 1e-3) / 1e12, 2), "unit": UNIT,
+                       "block": f"{g['spec'].m_local} rows x {g['spec'].n_local} columns per GPU",
+                       "plan": plan_text(g["plan"]), "spot_check_pass": g["ok"],
+                       "note": "the configuration's stated cut: b and b_scale along N only, a and a_scale replicated"}
         del g
+    elif world > 1:
+        column_only = {"grid": f"{stated[0]}x{stated[1]}", "note": "the chosen grid is the stated column-only cut: see value"}
 
     # The same GEMM with a and b in the harness's MN-major storage ([K][M], [K][N]), consumed in place.
     mn_ms = None
@@ -552,7 +555,7 @@ def run_ours(args):
             "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "e4m3fn x e4m3fn -> fp32 accumulate -> bf16", "data": "synthetic",
             "config": {"workload": f"fp8_block_scaled_gemm M={m_full} N={n} K={k}",
-                       "sharding": f"b and b_scale cut along N over {world} GPU(s), a and a_scale replicated: {m} rows x "
+                       "sharding": f"{chosen[0]} x {chosen[1]} grid of row x column blocks of c over {world} GPU(s): {m} rows x "
                                    f"{n_loc} columns per GPU, no collective, c left sharded",
                        "plan": plan_text(plan),
                        "l2": f"{nsets} rotating buffer sets of {set_bytes >> 20} MiB (> 2x L2) between launches",
@@ -572,8 +575,8 @@ def run_ours(args):
             "gpu_launches": args.steps,
             "clocks": clocks,
         }
-        if grid_run is not None:
-            line["row_column_grid"] = grid_run
+        if column_only is not None:
+            line["column_only"] = column_only
         if mn_ms is not None:
             line["mn_major_operands"] = {"ms_per_step": round(mn_ms, 5),
                                          "value": round(flops / (mn_ms * 1e-3) / 1e12, 2), "unit": UNIT}
@@ -597,8 +600,7 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-shape sweep")
     ap.add_argument("--shape", default="", help="M,N,K of another workload (for small profiler captures)")
-    ap.add_argument("--grid", default="", help="ROWSxCOLS grid of the ranks for the second figure "
-                                               "(default: the cost model's choice)")
+    ap.add_argument("--grid", default="", help="ROWSxCOLS grid of the ranks (default: the cost model's choice)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
