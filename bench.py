@@ -415,6 +415,12 @@ def run_ours(args):
     main_run = time_partition(pkg, ranks, m_full, n, k, chosen, rank, args.steps, args.warmup, dev)
     spec, sets, ms, ms_local = main_run["spec"], main_run["sets"], main_run["ms"], main_run["ms_local"]
     m, n_loc = spec.m_local, spec.n_local
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": f"M={m_full} N={n} K={k}", "ms_per_step": round(ms, 5),
+                              "plan": plan_text(main_run["plan"]), "spot_check_pass": main_run["ok"]}), flush=True)
+        ranks.close()
+        return
 
     # A loop long enough for the power cap to settle and for the clock sampler to see it (>= 1 s), beside the
     # K-step figure above, which at small K lasts a few milliseconds.
@@ -599,6 +605,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-shape sweep")
+    ap.add_argument("--profile", action="store_true",
+                    help="only the warm-up and the timed steps of the main workload (a small run to put a profiler on)")
     ap.add_argument("--shape", default="", help="M,N,K of another workload (for small profiler captures)")
     ap.add_argument("--grid", default="", help="ROWSxCOLS grid of the ranks (default: the cost model's choice)")
     args = ap.parse_args()
