@@ -74,7 +74,8 @@ typedef struct b200_fp8_mm_plan {
   int grid;       /* CTAs launched (persistent; a multiple of 2 when cta_pair)      */
   int tiles;      /* output tiles (x split_k = work items)                          */
   int smem_bytes; /* dynamic shared memory per CTA                                  */
-  int store_bufs; /* staging buffers per warpgroup for the TMA store of c: 1 or 2;
+  int store_bufs; /* staging buffers per warpgroup for the TMA store of c: 1 .. 4 (one per
+                     32-column box of the warpgroup's share stages the whole tile at once);
                      0 = plain stores (every tile split, or forced with -1)          */
   int full_tiles; /* output: tiles [0, full_tiles) run whole, the rest (the tail of a
                      partly filled last wave, or all tiles when there are few) are
@@ -141,8 +142,9 @@ int b200_fp8_mm_planned(const void* a, const void* b, const float* a_scale, cons
  *  a   element (i,kk) at a + i*a_sm + kk*a_sk; either a_sk == 1 (K-major, a_sm >= K) or
  *      a_sm == 1 (MN-major, a_sk >= M); the other stride a multiple of 16
  *  b   element (j,kk) at b + j*b_sn + kk*b_sk, same rule
- *  forced  NULL, or a plan as for b200_fp8_mm_planned; CTA pairs are available for
- *      K-major operands only (cta_pair = 1 with an MN-major operand: B200_FP8_MM_ERR_PLAN)
+ *  forced  NULL, or a plan as for b200_fp8_mm_planned. CTA pairs with an MN-major operand exist at
+ *      block_n 192 and 256 for a, and at block_n 256 for b; forcing cta_pair = 1 elsewhere gives
+ *      B200_FP8_MM_ERR_PLAN, and the automatic plan falls back to single CTAs there
  *
  * Everything else as for b200_fp8_mm. b200_fp8_mm_workspace_bytes covers both layouts.
  */
