@@ -58,6 +58,42 @@ __global__ void __launch_bounds__(256) rope_kernel(const __nv_bfloat16* __restri
   }
 }
 
+// The same with eight adjacent pair indices per thread: 16-byte loads and stores. Used when d2/2 is a multiple of 8
+// and every row start is 16-byte aligned (checked by the launcher).
+__global__ void __launch_bounds__(256) rope_kernel_vec8(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* y, int pos,
+                                                        int d0, int d1, int d2, long long xs1, long long xs2,
+                                                        long long ys1, long long ys2, int rows_per_block) {
+  const int half = d2 >> 1;
+  const int groups = half >> 3;  // groups of eight pair indices per position row
+  const long long g = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (g >= static_cast<long long>(d1) * groups) return;
+  const int i1 = static_cast<int>(g / groups);
+  const int j0 = static_cast<int>(g - static_cast<long long>(i1) * groups) * 8;
+  __nv_bfloat16 c[8], s[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) rope_angle(pos, i1, j0 + e, d2, &c[e], &s[e]);
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(d0, r0 + rows_per_block);
+  const __nv_bfloat16* xp = x + static_cast<long long>(i1) * xs2 + j0;
+  __nv_bfloat16* yp = y + static_cast<long long>(i1) * ys2 + j0;
+  for (int i0 = r0; i0 < r1; ++i0) {
+    const uint4 a = *reinterpret_cast<const uint4*>(xp + i0 * xs1);
+    const uint4 b = *reinterpret_cast<const uint4*>(xp + i0 * xs1 + half);
+    const __nv_bfloat16* x1 = reinterpret_cast<const __nv_bfloat16*>(&a);
+    const __nv_bfloat16* x2 = reinterpret_cast<const __nv_bfloat16*>(&b);
+    uint4 o1, o2;
+    __nv_bfloat16* y1 = reinterpret_cast<__nv_bfloat16*>(&o1);
+    __nv_bfloat16* y2 = reinterpret_cast<__nv_bfloat16*>(&o2);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      y1[e] = bsub(bmul(x1[e], c[e]), bmul(x2[e], s[e]));
+      y2[e] = badd(bmul(x2[e], c[e]), bmul(x1[e], s[e]));
+    }
+    *reinterpret_cast<uint4*>(yp + i0 * ys1) = o1;
+    *reinterpret_cast<uint4*>(yp + i0 * ys1 + half) = o2;
+  }
+}
+
 constexpr int kSoftmaxThreads = 512;
 
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
@@ -72,32 +108,108 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return __shfl_sync(0xffffffffu, t, 0);
 }
 
-// One CTA per row. Pass 1 reads the row (16-byte loads where the row is 16-byte aligned), forms e = expf(v * scale)
+// One CTA per row. Pass 1 reads the row (16-byte loads between the row's first and last 16-byte boundary), forms e = expf(v * scale)
 // and the fp32 row sum; pass 2 reads the row again (it is in L1/L2 now), rounds e to bf16 as the reference keeps
 // it, divides by the sum and writes in place. HBM sees one read and one write of the row.
 __global__ void __launch_bounds__(kSoftmaxThreads) div_softmax_kernel(__nv_bfloat16* qk, int sl, float scale) {
   __shared__ float scratch[kSoftmaxThreads / 32];
   __nv_bfloat16* row = qk + static_cast<long long>(blockIdx.x) * sl;
-  const bool vec = (reinterpret_cast<uintptr_t>(row) % 16) == 0;
-  const int sl_vec = vec ? (sl / 8) * 8 : 0;
+  // A row starts on a 2-byte boundary: `head` elements up to the next 16-byte boundary go one by one, then
+  // 16-byte pieces, then the rest.
+  const int head = min(sl, static_cast<int>(((16u - (reinterpret_cast<uintptr_t>(row) & 15u)) & 15u) >> 1));
+  const int body = ((sl - head) / 8) * 8;
+  __nv_bfloat16* vrow = row + head;
   float sum = 0.f;
-  for (int i = threadIdx.x * 8; i < sl_vec; i += kSoftmaxThreads * 8) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+  for (int i = threadIdx.x * 8; i < body; i += kSoftmaxThreads * 8) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(vrow + i);
     const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
 #pragma unroll
     for (int e = 0; e < 8; ++e) sum += expf(fl(v[e]) * scale);
   }
-  for (int i = sl_vec + threadIdx.x; i < sl; i += kSoftmaxThreads) sum += expf(fl(row[i]) * scale);
+  const int rest = sl - body;  // head + tail elements, at most 14
+  for (int t = threadIdx.x; t < rest; t += kSoftmaxThreads) {
+    const int i = t < head ? t : body + t;
+    sum += expf(fl(row[i]) * scale);
+  }
   const float total = block_sum(sum, scratch);
-  for (int i = threadIdx.x * 8; i < sl_vec; i += kSoftmaxThreads * 8) {
-    uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+  for (int i = threadIdx.x * 8; i < body; i += kSoftmaxThreads * 8) {
+    uint4 raw = *reinterpret_cast<const uint4*>(vrow + i);
     __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(&raw);
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = bf(__fdiv_rn(fl(bf(expf(fl(v[e]) * scale))), total));
-    *reinterpret_cast<uint4*>(row + i) = raw;
+    *reinterpret_cast<uint4*>(vrow + i) = raw;
   }
-  for (int i = sl_vec + threadIdx.x; i < sl; i += kSoftmaxThreads)
+  for (int t = threadIdx.x; t < rest; t += kSoftmaxThreads) {
+    const int i = t < head ? t : body + t;
     row[i] = bf(__fdiv_rn(fl(bf(expf(fl(row[i]) * scale))), total));
+  }
+}
+
+// Rows of up to kRegRowElems elements (the reference's own limit is 8192): the row is read ONCE, its exponentials
+// stay in registers (as the bf16 values the reference keeps) across the block-wide sum, and the quotients are
+// written back; four independent 16-byte loads per thread are in flight at a time.
+constexpr int kRegThreads = 256;
+constexpr int kRegVecs = 4;
+constexpr int kRegRowElems = kRegThreads * 8 * kRegVecs;  // 8192 elements in 16-byte pieces, + up to 14 stragglers
+
+__device__ __forceinline__ float block_sum_256(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < kRegThreads / 32) ? scratch[lane] : 0.f;
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return __shfl_sync(0xffffffffu, t, 0);
+}
+
+__global__ void __launch_bounds__(kRegThreads) div_softmax_regs_kernel(__nv_bfloat16* qk, int sl, float scale) {
+  __shared__ float scratch[kRegThreads / 32];
+  __nv_bfloat16* row = qk + static_cast<long long>(blockIdx.x) * sl;
+  const int head = min(sl, static_cast<int>(((16u - (reinterpret_cast<uintptr_t>(row) & 15u)) & 15u) >> 1));
+  const int body = ((sl - head) / 8) * 8;
+  const int rest = sl - body;  // head + tail elements, at most 14: one per thread
+  __nv_bfloat16* vrow = row + head;
+  uint4 raw[kRegVecs];
+#pragma unroll
+  for (int v = 0; v < kRegVecs; ++v) {
+    const int i = (static_cast<int>(threadIdx.x) + v * kRegThreads) * 8;
+    raw[v] = (i < body) ? *reinterpret_cast<const uint4*>(vrow + i) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  const int si = static_cast<int>(threadIdx.x) < head ? static_cast<int>(threadIdx.x) : body + static_cast<int>(threadIdx.x);
+  __nv_bfloat16 stray = bf(0.f);
+  float sum = 0.f;
+  if (static_cast<int>(threadIdx.x) < rest) {
+    const float e = expf(fl(row[si]) * scale);
+    sum += e;
+    stray = bf(e);
+  }
+#pragma unroll
+  for (int v = 0; v < kRegVecs; ++v) {
+    const int i = (static_cast<int>(threadIdx.x) + v * kRegThreads) * 8;
+    if (i < body) {
+      __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(&raw[v]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float ex = expf(fl(p[e]) * scale);
+        sum += ex;
+        p[e] = bf(ex);
+      }
+    }
+  }
+  const float total = block_sum_256(sum, scratch);
+#pragma unroll
+  for (int v = 0; v < kRegVecs; ++v) {
+    const int i = (static_cast<int>(threadIdx.x) + v * kRegThreads) * 8;
+    if (i < body) {
+      __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(&raw[v]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) p[e] = bf(__fdiv_rn(fl(p[e]), total));
+      *reinterpret_cast<uint4*>(vrow + i) = raw[v];
+    }
+  }
+  if (static_cast<int>(threadIdx.x) < rest) row[si] = bf(__fdiv_rn(fl(stray), total));
 }
 
 }  // namespace
@@ -108,7 +220,10 @@ int b200_mla_rope(const void* x, void* y, int pos, int d0, int d1, int d2, long 
                   long long ys1, long long ys2, void* stream) {
   if (x == nullptr || y == nullptr) return B200_FP8_MM_ERR_NULL;
   if (d0 <= 0 || d1 <= 0 || d2 <= 0 || (d2 & 1) != 0) return B200_FP8_MM_ERR_SHAPE;
-  const long long pairs = static_cast<long long>(d1) * (d2 / 2);
+  const int half = d2 / 2;
+  const bool vec8 = (half % 8) == 0 && (xs1 % 8) == 0 && (xs2 % 8) == 0 && (ys1 % 8) == 0 && (ys2 % 8) == 0 &&
+                    (reinterpret_cast<uintptr_t>(x) % 16) == 0 && (reinterpret_cast<uintptr_t>(y) % 16) == 0;
+  const long long pairs = static_cast<long long>(d1) * (vec8 ? half / 8 : half);
   const int threads = 256;
   const long long blocks_x = (pairs + threads - 1) / threads;
   if (blocks_x > 0x7fffffffll) return B200_FP8_MM_ERR_SHAPE;
@@ -119,10 +234,16 @@ int b200_mla_rope(const void* x, void* y, int pos, int d0, int d1, int d2, long 
   if (want_y > 65535) want_y = 65535;
   const int rows_per_block = static_cast<int>((d0 + want_y - 1) / want_y);
   const int blocks_y = (d0 + rows_per_block - 1) / rows_per_block;
-  rope_kernel<<<dim3(static_cast<unsigned>(blocks_x), static_cast<unsigned>(blocks_y)), threads, 0,
-                static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x),
-                                                     static_cast<__nv_bfloat16*>(y), pos, d0, d1, d2, xs1, xs2, ys1,
-                                                     ys2, rows_per_block);
+  const dim3 grid(static_cast<unsigned>(blocks_x), static_cast<unsigned>(blocks_y));
+  if (vec8) {
+    rope_kernel_vec8<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), pos, d0, d1, d2, xs1, xs2, ys1, ys2,
+        rows_per_block);
+  } else {
+    rope_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), pos, d0, d1, d2, xs1, xs2, ys1, ys2,
+        rows_per_block);
+  }
   if (cudaGetLastError() != cudaSuccess) return B200_FP8_MM_ERR_LAUNCH;
   return B200_FP8_MM_OK;
 }
@@ -133,8 +254,13 @@ int b200_mla_div_softmax(void* qk, int bs, int nh, int sl, int dnope, int drope,
   const long long rows = static_cast<long long>(bs) * nh;
   if (rows > 0x7fffffffll) return B200_FP8_MM_ERR_SHAPE;
   const float scale = 1.0f / sqrtf(static_cast<float>(dnope + drope));
-  div_softmax_kernel<<<static_cast<unsigned>(rows), kSoftmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16*>(qk), sl, scale);
+  if (sl <= kRegRowElems) {
+    div_softmax_regs_kernel<<<static_cast<unsigned>(rows), kRegThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16*>(qk), sl, scale);
+  } else {
+    div_softmax_kernel<<<static_cast<unsigned>(rows), kSoftmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<__nv_bfloat16*>(qk), sl, scale);
+  }
   if (cudaGetLastError() != cudaSuccess) return B200_FP8_MM_ERR_LAUNCH;
   return B200_FP8_MM_OK;
 }

@@ -392,6 +392,31 @@ def sweep_shapes(pkg, ranks, rank, dev, peaks, fp8_peak):
     return rows
 
 
+def mla_consumer_timings(pkg, dev, peaks):
+    """The two memory-bound kernels around the KV down-projection, at the reference model's decode sizes
+    (bs 128, 128 heads, 6144 cached positions + 1, rope width 64, KV row 576): GB/s of algorithmic bytes
+    (each element read once and written once) against the measured HBM copy bandwidth. Buffers are larger
+    than L2, so consecutive launches do not find their data there."""
+    bs, nh, sl, drope, dkv, msl = 128, 128, 6145, 64, 512, 8192
+    out = {}
+    qk = torch.randn(bs, nh, sl, device=dev, dtype=torch.float32).mul_(3).to(torch.bfloat16)
+    fn = lambda: pkg.div_softmax(qk, bs, nh, sl, 128, 64)
+    ms = time_launches([fn], 10, 3)
+    gbs = 2 * 2 * bs * nh * sl / (ms * 1e-3) / 1e9
+    out["div_softmax"] = {"shape": [bs, nh, sl], "ms": round(ms, 4), "gbs": round(gbs, 1),
+                          "pct_hbm_measured": round(100 * gbs / peaks["hbm_gbs"], 1)}
+    del qk
+    cache = torch.randn(bs, msl, dkv + drope, device=dev, dtype=torch.bfloat16)
+    kr = torch.empty(bs, sl, drope, device=dev, dtype=torch.bfloat16)
+    fn = lambda: pkg.mla_decode(cache, kr, 0, dkv, 0, bs, sl, drope, msl * (dkv + drope), dkv + drope, sl * drope, drope)
+    ms = time_launches([fn], 10, 3)
+    gbs = 2 * 2 * bs * sl * drope / (ms * 1e-3) / 1e9
+    out["rope_keys"] = {"shape": [bs, sl, drope], "ms": round(ms, 4), "gbs": round(gbs, 1),
+                        "pct_hbm_measured": round(100 * gbs / peaks["hbm_gbs"], 1),
+                        "note": "128-byte runs gathered out of 1152-byte KV-cache rows"}
+    return out
+
+
 def run_ours(args):
     import amd_developer_challenge_2025_b200 as pkg
     from amd_developer_challenge_2025_b200.fp8_mm import check_device_status
@@ -541,8 +566,11 @@ def run_ours(args):
     del sets, main_run
 
     per_shape = []
+    mla = None
     if not args.no_sweep and not args.shape:
         per_shape = sweep_shapes(pkg, ranks, rank, dev, peaks, fp8_peak)
+        if world == 1:
+            mla = mla_consumer_timings(pkg, dev, peaks)
 
     cpu_baseline = None
     if rank == 0 and world == 1:
@@ -593,6 +621,8 @@ def run_ours(args):
             line["all_gather_c"] = gather
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
+        if mla is not None:
+            line["mla_consumers"] = mla
         if per_shape:
             line["per_shape"] = per_shape
         print(json.dumps(line), flush=True)

@@ -42,6 +42,18 @@ def test_rope_contiguous(d0, d1, d2, pos):
     assert_rope_close(y, mla_oracle.rope_3d(x, pos))
 
 
+def test_rope_unaligned_strides_take_the_scalar_kernel():
+    """Rows that do not start on 16-byte boundaries (a column slice at an odd offset, odd row pitch)."""
+    d0, d1, d2, pos = 5, 33, 64, 9
+    wide = bf16_randn(d0, d1, d2 + 3, seed=4)
+    dwide = wide.cuda()
+    out = torch.full((d0, d1, d2 + 5), float("nan"), dtype=torch.bfloat16, device="cuda")
+    pkg.mla_decode(dwide, out, pos, 1, 3, d0, d1, d2, d1 * (d2 + 3), d2 + 3, d1 * (d2 + 5), d2 + 5)
+    torch.cuda.synchronize()
+    assert_rope_close(out[:, :, 3:3 + d2], mla_oracle.rope_3d(wide[:, :, 1:1 + d2], pos))
+    assert torch.isnan(out[:, :, :3].float()).all() and torch.isnan(out[:, :, 3 + d2:].float()).all()
+
+
 def test_rope_as_the_reference_calls_it():
     """The two call sites of the reference (3-amd-mla-decode/amd-mla-submission.py:265, 273): the query's rope
     part rotated in place inside [bs*nh, sl, dnope+drope], and the key's rope part gathered out of the KV cache
