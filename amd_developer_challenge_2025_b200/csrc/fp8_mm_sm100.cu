@@ -85,6 +85,9 @@ struct KernelParams {
   int tiles_m, tiles_n, split_k, kblocks;
   int full_tiles;  // tiles [0, full_tiles) run unsplit; the rest are split split_k ways along K
   int raster_group;
+  // Reciprocals for decode_work's divisions (see div_small): 1 / (raster_group * tiles_n), 1 / raster_group,
+  // 1 / (rows of the last, shorter raster group), 1 / split_k, 1 / (tiles_m * tiles_n).
+  float rcp_per_group, rcp_raster, rcp_raster_last, rcp_split, rcp_per_problem;
   int b_scale_rows;
   int vec_store;  // 1 when c, ldc and N allow 16-byte stores
   int stages;
@@ -539,6 +542,22 @@ struct WorkItem {
   bool skip;
 };
 
+// n / d for 0 <= n < 2^22 and d >= 1, with rcp = 1.0f / d: the float quotient is off by at most one, which the
+// remainder corrects. Every role decodes one work item per tile; the hardware has no integer divide, and the
+// compiler's division sequences (the 64-bit ones above all) cost about a thousand clocks per item, which tiles of
+// two to four K blocks feel.
+__device__ __forceinline__ int div_small(int n, int d, float rcp) {
+  int q = __float2int_rz(__int2float_rn(n) * rcp);
+  const int r = n - q * d;
+  if (r < 0) {
+    --q;
+  } else if (r >= d) {
+    ++q;
+  }
+  return q;
+}
+constexpr int kDivSmallLimit = 1 << 22;
+
 // Work item w -> tile and K range. Tiles are walked in groups of raster_group tile rows, column
 // by column inside a group, so that the CTAs running at one time share A and B tiles in L2.
 template <bool GENERIC>
@@ -553,31 +572,42 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& p, int w, in
     // The tail: tiles that would fill only part of a last wave are cut along K so that every CTA
     // gets a share of them.
     const int r = w - p.full_tiles;
-    t = p.full_tiles + r / p.split_k;
-    it.split = r % p.split_k;
+    const int q = (r < kDivSmallLimit) ? div_small(r, p.split_k, p.rcp_split) : r / p.split_k;
+    t = p.full_tiles + q;
+    it.split = r - q * p.split_k;
     it.nsplit = p.split_k;
   }
+  const bool small = t < kDivSmallLimit;
   it.tile = t;
   it.group = 0;
   it.m_limit = p.M;
   if (GENERIC && p.groups > 0) {
     const int per_problem = p.tiles_m * p.tiles_n;
-    it.group = t / per_problem;
+    it.group = small ? div_small(t, per_problem, p.rcp_per_problem) : t / per_problem;
     t -= it.group * per_problem;
     if (p.m_valid != nullptr) it.m_limit = max(0, min(p.M, __ldg(p.m_valid + it.group)));
   }
   const int per_group = p.raster_group * p.tiles_n;
-  const int group = t / per_group;
+  const int group = small ? div_small(t, per_group, p.rcp_per_group) : t / per_group;
   const int first_m = group * p.raster_group;
-  const int gsize = min(p.raster_group, p.tiles_m - first_m);
+  const bool whole = first_m + p.raster_group <= p.tiles_m;
+  const int gsize = whole ? p.raster_group : p.tiles_m - first_m;
   const int within = t - group * per_group;
-  const int tm = first_m + within % gsize;
-  const int tn = within / gsize;
+  const int tn = small ? div_small(within, gsize, whole ? p.rcp_raster : p.rcp_raster_last) : within / gsize;
+  const int tm = first_m + (within - tn * gsize);
   it.m0 = tm * tile_m;
   it.n0 = tn * block_n;
   it.skip = GENERIC && it.m0 >= it.m_limit;
-  it.kb_begin = static_cast<int>((static_cast<long long>(it.split) * p.kblocks) / it.nsplit);
-  it.kb_end = static_cast<int>((static_cast<long long>(it.split + 1) * p.kblocks) / it.nsplit);
+  if (it.nsplit == 1) {
+    it.kb_begin = 0;
+    it.kb_end = p.kblocks;
+  } else {
+    // split < nsplit <= 64 and kblocks < 2^24: the products fit 32 bits
+    it.kb_begin = static_cast<int>((static_cast<unsigned>(it.split) * static_cast<unsigned>(p.kblocks)) /
+                                   static_cast<unsigned>(it.nsplit));
+    it.kb_end = static_cast<int>((static_cast<unsigned>(it.split + 1) * static_cast<unsigned>(p.kblocks)) /
+                                 static_cast<unsigned>(it.nsplit));
+  }
   return it;
 }
 
@@ -910,6 +940,25 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 #pragma unroll
       for (int j = 0; j < (kScalarCols > 0 ? kScalarCols : 1); ++j) accf[j] = 0.f;
 
+      // One K block's fmas on CC landed columns starting at column offset ch * CC of this thread's share.
+      auto fma_cols = [&](auto& vv, int ch, float slo, float shi) {
+        constexpr int CC = sizeof(vv) / sizeof(uint32_t);
+        // 32 columns at a time: a scale-row boundary can fall on any multiple of 32 columns
+#pragma unroll
+        for (int q = 0; q < CC / 32; ++q) {
+          const int cb = ch * CC + 32 * q;  // offset inside this thread's columns
+          const float s = (((gcol0 + cb) >> 7) == jb0) ? slo : shi;
+          if (cb < kPackedCols) {
+            const unsigned long long s2 = pack2(s, s);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) fma2(acc2[cb / 2 + j], vv[32 * q + 2 * j], vv[32 * q + 2 * j + 1], s2);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              accf[cb - kPackedCols + j] = fmaf(__uint_as_float(vv[32 * q + j]), s, accf[cb - kPackedCols + j]);
+          }
+        }
+      };
       for (int kb0 = it.kb_begin; kb0 < it.kb_end && ok; kb0 += kScaleGroup) {
         // Scales of the next (up to) four K blocks: three 16-byte shared-memory loads, then the
         // slot goes back to the loader.
@@ -982,24 +1031,10 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 ready_next = mbar_test(ready_base + static_cast<uint32_t>(ns * 8), np);
               }
             }
-            // 32 columns at a time: a scale-row boundary can fall on any multiple of 32 columns
 #ifdef FP8MM_X_NOPROMO
             if (ch > 0) continue;
 #endif
-#pragma unroll
-            for (int q = 0; q < CC / 32; ++q) {
-              const int cb = ch * CC + 32 * q;  // offset inside this thread's columns
-              const float s = (((gcol0 + cb) >> 7) == jb0) ? s_lo[u] : s_hi[u];
-              if (cb < kPackedCols) {
-                const unsigned long long s2 = pack2(s, s);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) fma2(acc2[cb / 2 + j], v[32 * q + 2 * j], v[32 * q + 2 * j + 1], s2);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  accf[cb - kPackedCols + j] = fmaf(__uint_as_float(v[32 * q + j]), s, accf[cb - kPackedCols + j]);
-              }
-            }
+            fma_cols(v, ch, s_lo[u], s_hi[u]);
 #ifndef FP8MM_X_NOPROMO
             if (ch + 1 < Cfg::kChunks) tmem_ld(taddr + static_cast<uint32_t>((ch + 1) * CC), v);
 #endif
@@ -1086,6 +1121,9 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const int sw = (row_in_tile >> 1) & 3;
         constexpr int kBoxes = Cfg::kColsPerThread / kStoreBoxCols;
         auto stage_box = [&](int ch, int bufi) {
+#ifdef FP8MM_X_NOSTAGE
+          return;
+#endif
           uint8_t* rowp = my_stage + bufi * kStoreBufBytes + row_in_tile * 64;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -1099,6 +1137,9 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           }
         };
         auto store_box = [&](int ch, int bufi) {
+#ifdef FP8MM_X_NOSTOREISSUE
+          return;
+#endif
           if (GENERIC && p.groups > 0) {
             tma_store_3d(&tmap_c, smem_u32(my_stage + bufi * kStoreBufBytes), col0 + ch * kStoreBoxCols,
                          it.m0 + static_cast<int>(cta_rank) * kBlockM, it.group);
@@ -1110,16 +1151,20 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         if (p.store_bufs >= kBoxes) {
           // A staging buffer for every box of the warpgroup's share: the whole share is staged between two
           // barriers and leaves as kBoxes bulk stores that drain while the next tile's K loop runs; the
-          // wait below is for the previous tile's stores, issued a tile ago.
-          if (wg_tid == 0) tma_store_wait_read<0>();
+          // wait below is for the previous tile's stores, issued a tile ago. Box ch is issued (and later waited
+          // for) by lane 0 of the warpgroup's warp ch % 4: a bulk store costs its issuing thread about 200
+          // clocks, which four warps pay side by side instead of one thread four times in a row.
+          if (lane == 0) tma_store_wait_read<0>();
           wg_bar_sync(half);
 #pragma unroll
           for (int ch = 0; ch < kBoxes; ++ch) stage_box(ch, ch);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           wg_bar_sync(half);
-          if (wg_tid == 0 && *abort_flag == 0) {
+          if (lane == 0 && *abort_flag == 0) {
 #pragma unroll
-            for (int ch = 0; ch < kBoxes; ++ch) store_box(ch, ch);
+            for (int ch = 0; ch < kBoxes; ++ch) {
+              if ((ch & 3) == (wg_tid >> 5)) store_box(ch, ch);
+            }
           }
         } else {
 #pragma unroll
@@ -1169,7 +1214,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
   if (warp >= 4) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");  // none in flight past here
     // the staging buffers must outlive the bulk stores that read them
-    if ((threadIdx.x & 127) == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // each group's issuer
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every thread that issued stores
   }
   // Teardown: every role has left its loop (normally or through an expired wait). In a pair no
   // CTA may exit while its peer can still signal its barriers or use its shared memory.
@@ -1544,13 +1589,26 @@ double choose_plan(int M, int N, int K, int sm_count, const b200_fp8_mm_plan* fo
   return best.cost;
 }
 
+// The reciprocals decode_work divides with (tiles_m, tiles_n, split_k, raster_group and groups are set).
+void set_decode_reciprocals(KernelParams& kp) {
+  const int last = kp.tiles_m % kp.raster_group;
+  kp.rcp_per_group = 1.0f / static_cast<float>(kp.raster_group * kp.tiles_n);
+  kp.rcp_raster = 1.0f / static_cast<float>(kp.raster_group);
+  kp.rcp_raster_last = 1.0f / static_cast<float>(last > 0 ? last : kp.raster_group);
+  kp.rcp_split = 1.0f / static_cast<float>(kp.split_k > 0 ? kp.split_k : 1);
+  kp.rcp_per_problem = 1.0f / static_cast<float>(kp.tiles_m * kp.tiles_n);
+}
+
+// decode_work forms (split + 1) * kblocks in 32 bits; the selector itself never splits more than 16 ways.
+constexpr int kMaxSplitK = 64;
+
 bool plan_is_supported(const b200_fp8_mm_plan& pl, int kblocks) {
   if (!valid_block_n(pl.block_n)) return false;
   if (pl.cta_pair != 0 && pl.cta_pair != 1) return false;
   if (pl.stages < 2 || pl.stages > kMaxStages) return false;
   if (pl.store_bufs < 0 || pl.store_bufs > 4) return false;
   if (pl.smem_bytes > kMaxSmem) return false;
-  if (pl.split_k < 1 || pl.split_k > kblocks) return false;
+  if (pl.split_k < 1 || pl.split_k > kblocks || pl.split_k > kMaxSplitK) return false;
   if (pl.split_k > 1 && (pl.tiles - pl.full_tiles) * (pl.cta_pair ? 2 : 1) > kMaxCounters) return false;
   if (pl.full_tiles < 0 || pl.full_tiles > pl.tiles) return false;
   return true;
@@ -1748,6 +1806,7 @@ int run(const void* a, const void* b, const float* a_scale, const float* b_scale
     if (g > 16) g = 16;
     kp.raster_group = g;
   }
+  set_decode_reciprocals(kp);
   kp.b_scale_rows = ceil_div(N + n_phase, 128);
   kp.vec_store =
       ((reinterpret_cast<uintptr_t>(c) % 16) == 0 && (ldc % 8) == 0 && (N % 8) == 0) ? 1 : 0;
@@ -1908,6 +1967,7 @@ int run_grouped(const void* a, const void* b, const float* a_scale, const float*
     if (g > 16) g = 16;
     kp.raster_group = g;
   }
+  set_decode_reciprocals(kp);
   kp.b_scale_rows = ceil_div(N, 128);
   kp.vec_store = ((reinterpret_cast<uintptr_t>(c) % 16) == 0 && (ldc % 8) == 0 && (c_g % 8) == 0 && (N % 8) == 0) ? 1 : 0;
   kp.wait_limit_ns = kWaitLimitNs;
