@@ -327,7 +327,8 @@ _host_pipelines: dict[int, _HostPipeline] = {}
 def host_row_chunks(m: int, chunk_rows: int = 1024) -> list[tuple[int, int]]:
     """Row ranges [r0, r1) the host entry point cuts a problem into: a short first range, so that the
     first copy of c back to the host can start as early as possible, then `chunk_rows` rows each
-    (multiples of 128, the kernel's row block)."""
+    (multiples of 128, the kernel's row block), and a short last range, because the last range's GEMM and
+    its copy back to the host are the part of the call that nothing else overlaps."""
     if m <= 512:
         return [(0, m)]
     out = [(0, 256)]
@@ -335,6 +336,10 @@ def host_row_chunks(m: int, chunk_rows: int = 1024) -> list[tuple[int, int]]:
     while r < m:
         out.append((r, min(m, r + chunk_rows)))
         r += chunk_rows
+    r0, r1 = out[-1]
+    if r1 - r0 > 256:
+        out[-1] = (r0, r1 - 256)
+        out.append((r1 - 256, r1))
     return out
 
 

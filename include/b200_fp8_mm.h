@@ -69,7 +69,8 @@ typedef struct b200_fp8_mm_plan {
   int block_m;    /* rows of C per CTA (128)                                        */
   int block_n;    /* columns of C per tile: 64, 128, 192 or 256                     */
   int cta_pair;   /* 1: two CTAs share a 256-row tile through cta_group::2          */
-  int split_k;    /* number of K ranges per split tile (1 = no tile is split)       */
+  int split_k;    /* number of K ranges per split tile (1 = no tile is split; the
+                     selector uses at most 16, a forced plan at most 64)            */
   int stages;     /* depth of the TMA -> shared memory ring                         */
   int grid;       /* CTAs launched (persistent; a multiple of 2 when cta_pair)      */
   int tiles;      /* output tiles (x split_k = work items)                          */

@@ -160,3 +160,17 @@ def test_runner_spec_parser_and_grid():
     assert sorted({m for (m, _, _, _) in grid}) == [1024, 6144]
     assert {(n, k) for (m, n, k, _) in grid if m == 1024} == {(n, k) for (m, n, k, _) in grid if m == 6144}
     assert len({(n, k) for (_, n, k, _) in grid}) == 9 and len({s for (*_, s) in grid}) == 18
+
+
+def test_host_row_ranges_cover_the_rows_in_order():
+    from amd_developer_challenge_2025_b200.fp8_mm import host_row_chunks
+    for m in (1, 128, 512, 640, 1024, 2304, 8192, 8192 + 128, 16384):
+        for chunk in (256, 512, 1024, 4096):
+            ranges = host_row_chunks(m, chunk)
+            assert ranges[0][0] == 0 and ranges[-1][1] == m
+            assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+            assert all(r0 < r1 for r0, r1 in ranges)
+            assert all(r0 % 128 == 0 for r0, _ in ranges)
+            if m > 512:
+                assert ranges[0] == (0, 256)                 # the first copy back can start early
+                assert ranges[-1][1] - ranges[-1][0] <= max(256, chunk // 2) or chunk <= 256

@@ -313,6 +313,21 @@ def test_host_buffer_entry_point():
     assert_close(c, oracle.dequant_matmul(a, b, a_s, b_s), "host entry")
 
 
+def test_host_buffer_entry_point_streams_row_ranges():
+    # several row ranges (short first and last ones), pinned buffers, twice over the cached device buffers
+    from amd_developer_challenge_2025_b200.fp8_mm import host_row_chunks
+    m, n, k = 2304, 576, 512
+    assert len(host_row_chunks(m, 512)) >= 5
+    a, b, a_s, b_s, c = (t.pin_memory() for t in pkg.make_inputs(m, n, k, 13))
+    ref = oracle.dequant_matmul(a, b, a_s, b_s)
+    for _ in range(2):
+        c.zero_()
+        out = pkg.fp8_mm_host(a, b, a_s, b_s, c, chunk_rows=512)
+        assert out is c
+        assert_close(c, ref, "host entry, row ranges")
+    check_device_status()
+
+
 def test_non_default_stream_and_back_to_back_launches():
     m, n, k = 512, 1024, 1024
     a, b, a_s, b_s, c = cuda_inputs(m, n, k, 6)
