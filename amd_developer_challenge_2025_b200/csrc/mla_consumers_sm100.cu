@@ -71,26 +71,60 @@ __global__ void __launch_bounds__(256) rope_kernel_vec8(const __nv_bfloat16* __r
   const int j0 = static_cast<int>(g - static_cast<long long>(i1) * groups) * 8;
   __nv_bfloat16 c[8], s[8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) rope_angle(pos, i1, j0 + e, d2, &c[e], &s[e]);
+  for (int e = 0; e < 8; ++e) {
+    __nv_bfloat16 ce, se;
+    rope_angle(pos, i1, j0 + e, d2, &ce, &se);
+    c[e] = ce;
+    s[e] = se;
+  }
   const int r0 = blockIdx.y * rows_per_block;
   const int r1 = min(d0, r0 + rows_per_block);
   const __nv_bfloat16* xp = x + static_cast<long long>(i1) * xs2 + j0;
   __nv_bfloat16* yp = y + static_cast<long long>(i1) * ys2 + j0;
-  for (int i0 = r0; i0 < r1; ++i0) {
-    const uint4 a = *reinterpret_cast<const uint4*>(xp + i0 * xs1);
-    const uint4 b = *reinterpret_cast<const uint4*>(xp + i0 * xs1 + half);
-    const __nv_bfloat16* x1 = reinterpret_cast<const __nv_bfloat16*>(&a);
-    const __nv_bfloat16* x2 = reinterpret_cast<const __nv_bfloat16*>(&b);
-    uint4 o1, o2;
-    __nv_bfloat16* y1 = reinterpret_cast<__nv_bfloat16*>(&o1);
-    __nv_bfloat16* y2 = reinterpret_cast<__nv_bfloat16*>(&o2);
+  // Four rows at a time: their eight 16-byte loads are issued before the first result is stored, so a thread keeps
+  // 128 bytes in flight instead of 32 (in place is still fine: a row's loads precede its own stores, and rows do
+  // not overlap).
+  constexpr int kRowsInFlight = 4;
+  // The rotation in packed bf16 arithmetic (two elements per instruction). The hardware's bf16 multiply, add and
+  // subtract round the exact result once; rounding the fp32 result of the same operation to bf16, which is what
+  // the reference's arithmetic amounts to, gives the same value (a bf16 product is exact in fp32, and fp32 carries
+  // more than twice bf16's precision plus two bits, so the double rounding of a sum is harmless). The _rn forms
+  // are never contracted into a fused multiply-add, which would skip the products' rounding.
+  __nv_bfloat162 c2[4], s2[4];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      y1[e] = bsub(bmul(x1[e], c[e]), bmul(x2[e], s[e]));
-      y2[e] = badd(bmul(x2[e], c[e]), bmul(x1[e], s[e]));
+  for (int e = 0; e < 4; ++e) {
+    c2[e] = __halves2bfloat162(c[2 * e], c[2 * e + 1]);
+    s2[e] = __halves2bfloat162(s[2 * e], s[2 * e + 1]);
+  }
+  auto rotate_store = [&](const uint4& a, const uint4& b, int i0) {
+    const __nv_bfloat162* x1 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+    uint4 o1, o2;
+    __nv_bfloat162* y1 = reinterpret_cast<__nv_bfloat162*>(&o1);
+    __nv_bfloat162* y2 = reinterpret_cast<__nv_bfloat162*>(&o2);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      y1[e] = __hsub2_rn(__hmul2_rn(x1[e], c2[e]), __hmul2_rn(x2[e], s2[e]));
+      y2[e] = __hadd2_rn(__hmul2_rn(x2[e], c2[e]), __hmul2_rn(x1[e], s2[e]));
     }
     *reinterpret_cast<uint4*>(yp + i0 * ys1) = o1;
     *reinterpret_cast<uint4*>(yp + i0 * ys1 + half) = o2;
+  };
+  int i0 = r0;
+  for (; i0 + kRowsInFlight <= r1; i0 += kRowsInFlight) {
+    uint4 a[kRowsInFlight], b[kRowsInFlight];
+#pragma unroll
+    for (int u = 0; u < kRowsInFlight; ++u) {
+      a[u] = *reinterpret_cast<const uint4*>(xp + (i0 + u) * xs1);
+      b[u] = *reinterpret_cast<const uint4*>(xp + (i0 + u) * xs1 + half);
+    }
+#pragma unroll
+    for (int u = 0; u < kRowsInFlight; ++u) rotate_store(a[u], b[u], i0 + u);
+  }
+  for (; i0 < r1; ++i0) {
+    const uint4 a = *reinterpret_cast<const uint4*>(xp + i0 * xs1);
+    const uint4 b = *reinterpret_cast<const uint4*>(xp + i0 * xs1 + half);
+    rotate_store(a, b, i0);
   }
 }
 
@@ -108,10 +142,26 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return __shfl_sync(0xffffffffu, t, 0);
 }
 
+// exp(v * scale) as 2^(v * scale * log2 e) with the hardware's exponential (ex2.approx: relative error about
+// 2^-22, far inside the bf16 rounding that follows). The correctly rounded expf and the IEEE division of the
+// first version cost some thirty instructions per element and made the kernel compute-bound at half the HBM rate.
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// The two bf16 halves of a 32-bit word as floats, and back (one cvt.rn.bf16x2.f32).
+__device__ __forceinline__ float lo_f(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_f(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 // One CTA per row. Pass 1 reads the row (16-byte loads between the row's first and last 16-byte boundary), forms e = expf(v * scale)
 // and the fp32 row sum; pass 2 reads the row again (it is in L1/L2 now), rounds e to bf16 as the reference keeps
 // it, divides by the sum and writes in place. HBM sees one read and one write of the row.
-__global__ void __launch_bounds__(kSoftmaxThreads) div_softmax_kernel(__nv_bfloat16* qk, int sl, float scale) {
+__global__ void __launch_bounds__(kSoftmaxThreads) div_softmax_kernel(__nv_bfloat16* qk, int sl, float scale2) {
   __shared__ float scratch[kSoftmaxThreads / 32];
   __nv_bfloat16* row = qk + static_cast<long long>(blockIdx.x) * sl;
   // A row starts on a 2-byte boundary: `head` elements up to the next 16-byte boundary go one by one, then
@@ -122,26 +172,31 @@ __global__ void __launch_bounds__(kSoftmaxThreads) div_softmax_kernel(__nv_bfloa
   float sum = 0.f;
   for (int i = threadIdx.x * 8; i < body; i += kSoftmaxThreads * 8) {
     const uint4 raw = *reinterpret_cast<const uint4*>(vrow + i);
-    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int e = 0; e < 8; ++e) sum += expf(fl(v[e]) * scale);
+    for (int e = 0; e < 4; ++e) sum += exp2_fast(lo_f(w[e]) * scale2) + exp2_fast(hi_f(w[e]) * scale2);
   }
   const int rest = sl - body;  // head + tail elements, at most 14
   for (int t = threadIdx.x; t < rest; t += kSoftmaxThreads) {
     const int i = t < head ? t : body + t;
-    sum += expf(fl(row[i]) * scale);
+    sum += exp2_fast(fl(row[i]) * scale2);
   }
-  const float total = block_sum(sum, scratch);
+  const float inv = 1.0f / block_sum(sum, scratch);
   for (int i = threadIdx.x * 8; i < body; i += kSoftmaxThreads * 8) {
-    uint4 raw = *reinterpret_cast<const uint4*>(vrow + i);
-    __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(&raw);
+    const uint4 raw = *reinterpret_cast<const uint4*>(vrow + i);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[4];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = bf(__fdiv_rn(fl(bf(expf(fl(v[e]) * scale))), total));
-    *reinterpret_cast<uint4*>(vrow + i) = raw;
+    for (int e = 0; e < 4; ++e) {
+      // e rounded to bf16 as the reference keeps it, then the quotient rounded to bf16
+      const uint32_t e16 = pack_bf16(exp2_fast(lo_f(w[e]) * scale2), exp2_fast(hi_f(w[e]) * scale2));
+      o[e] = pack_bf16(lo_f(e16) * inv, hi_f(e16) * inv);
+    }
+    *reinterpret_cast<uint4*>(vrow + i) = make_uint4(o[0], o[1], o[2], o[3]);
   }
   for (int t = threadIdx.x; t < rest; t += kSoftmaxThreads) {
     const int i = t < head ? t : body + t;
-    row[i] = bf(__fdiv_rn(fl(bf(expf(fl(row[i]) * scale))), total));
+    row[i] = bf(fl(bf(exp2_fast(fl(row[i]) * scale2))) * inv);
   }
 }
 
@@ -164,7 +219,7 @@ __device__ __forceinline__ float block_sum_256(float v, float* scratch) {
   return __shfl_sync(0xffffffffu, t, 0);
 }
 
-__global__ void __launch_bounds__(kRegThreads) div_softmax_regs_kernel(__nv_bfloat16* qk, int sl, float scale) {
+__global__ void __launch_bounds__(kRegThreads, 8) div_softmax_regs_kernel(__nv_bfloat16* qk, int sl, float scale2) {
   __shared__ float scratch[kRegThreads / 32];
   __nv_bfloat16* row = qk + static_cast<long long>(blockIdx.x) * sl;
   const int head = min(sl, static_cast<int>(((16u - (reinterpret_cast<uintptr_t>(row) & 15u)) & 15u) >> 1));
@@ -181,7 +236,7 @@ __global__ void __launch_bounds__(kRegThreads) div_softmax_regs_kernel(__nv_bflo
   __nv_bfloat16 stray = bf(0.f);
   float sum = 0.f;
   if (static_cast<int>(threadIdx.x) < rest) {
-    const float e = expf(fl(row[si]) * scale);
+    const float e = exp2_fast(fl(row[si]) * scale2);
     sum += e;
     stray = bf(e);
   }
@@ -189,27 +244,27 @@ __global__ void __launch_bounds__(kRegThreads) div_softmax_regs_kernel(__nv_bflo
   for (int v = 0; v < kRegVecs; ++v) {
     const int i = (static_cast<int>(threadIdx.x) + v * kRegThreads) * 8;
     if (i < body) {
-      __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(&raw[v]);
+      uint32_t* w = reinterpret_cast<uint32_t*>(&raw[v]);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float ex = expf(fl(p[e]) * scale);
-        sum += ex;
-        p[e] = bf(ex);
+      for (int e = 0; e < 4; ++e) {
+        const float a = exp2_fast(lo_f(w[e]) * scale2), b = exp2_fast(hi_f(w[e]) * scale2);
+        sum += a + b;
+        w[e] = pack_bf16(a, b);  // kept as the bf16 values the reference stores
       }
     }
   }
-  const float total = block_sum_256(sum, scratch);
+  const float inv = 1.0f / block_sum_256(sum, scratch);
 #pragma unroll
   for (int v = 0; v < kRegVecs; ++v) {
     const int i = (static_cast<int>(threadIdx.x) + v * kRegThreads) * 8;
     if (i < body) {
-      __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(&raw[v]);
+      uint32_t* w = reinterpret_cast<uint32_t*>(&raw[v]);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) p[e] = bf(__fdiv_rn(fl(p[e]), total));
+      for (int e = 0; e < 4; ++e) w[e] = pack_bf16(lo_f(w[e]) * inv, hi_f(w[e]) * inv);
       *reinterpret_cast<uint4*>(vrow + i) = raw[v];
     }
   }
-  if (static_cast<int>(threadIdx.x) < rest) row[si] = bf(__fdiv_rn(fl(stray), total));
+  if (static_cast<int>(threadIdx.x) < rest) row[si] = bf(fl(stray) * inv);
 }
 
 }  // namespace
@@ -228,7 +283,7 @@ int b200_mla_rope(const void* x, void* y, int pos, int d0, int d1, int d2, long 
   const long long blocks_x = (pairs + threads - 1) / threads;
   if (blocks_x > 0x7fffffffll) return B200_FP8_MM_ERR_SHAPE;
   // enough CTAs for every SM a few times over, without cutting d0 finer than 4 rows per CTA
-  long long want_y = (148 * 8 + blocks_x - 1) / blocks_x;
+  long long want_y = (148 * 2 + blocks_x - 1) / blocks_x;
   if (want_y > (d0 + 3) / 4) want_y = (d0 + 3) / 4;
   if (want_y < 1) want_y = 1;
   if (want_y > 65535) want_y = 65535;
@@ -253,13 +308,14 @@ int b200_mla_div_softmax(void* qk, int bs, int nh, int sl, int dnope, int drope,
   if (bs <= 0 || nh <= 0 || sl <= 0 || dnope + drope <= 0) return B200_FP8_MM_ERR_SHAPE;
   const long long rows = static_cast<long long>(bs) * nh;
   if (rows > 0x7fffffffll) return B200_FP8_MM_ERR_SHAPE;
-  const float scale = 1.0f / sqrtf(static_cast<float>(dnope + drope));
+  // exp(v / sqrt(d)) = 2^(v * scale2)
+  const float scale2 = 1.4426950408889634f / sqrtf(static_cast<float>(dnope + drope));
   if (sl <= kRegRowElems) {
     div_softmax_regs_kernel<<<static_cast<unsigned>(rows), kRegThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__nv_bfloat16*>(qk), sl, scale);
+        static_cast<__nv_bfloat16*>(qk), sl, scale2);
   } else {
     div_softmax_kernel<<<static_cast<unsigned>(rows), kSoftmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<__nv_bfloat16*>(qk), sl, scale);
+        static_cast<__nv_bfloat16*>(qk), sl, scale2);
   }
   if (cudaGetLastError() != cudaSuccess) return B200_FP8_MM_ERR_LAUNCH;
   return B200_FP8_MM_OK;

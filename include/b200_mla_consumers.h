@@ -34,9 +34,11 @@ int b200_mla_rope(const void* x, void* y, int pos, int d0, int d1, int d2,
 /*
  * In-place softmax over the last dimension of the contiguous bf16 tensor qk [bs][nh][sl], of
  * qk / sqrt(dnope + drope). Replaces `div_softmax(qk, bs, nh, sl, dnope, drope)` and div_softmax_kernel
- * (3-amd-mla-decode/amd-mla-submission.py:10, 127-225), with its arithmetic: e = expf(float(v) * scale)
+ * (3-amd-mla-decode/amd-mla-submission.py:10, 127-225), with its arithmetic: e = exp(float(v) * scale)
  * with no maximum subtracted, the row sum adds e in fp32, the result is bf16(float(bf16(e)) / sum).
- * Any sl (the reference's kernel stops at 8192).
+ * The exponential is the hardware's 2^x (relative error about 2^-22) and the quotient a multiplication
+ * by 1 / sum: a result can differ from a correctly rounded evaluation by one bf16 step, the same as
+ * between two math libraries. Any sl (the reference's kernel stops at 8192).
  */
 int b200_mla_div_softmax(void* qk, int bs, int nh, int sl, int dnope, int drope, void* stream);
 
