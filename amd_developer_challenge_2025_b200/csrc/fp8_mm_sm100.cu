@@ -915,6 +915,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 
     int buf = 0, slot = 0, cstage = 0;
     uint32_t ready_next = 0;  // kEarlyProbe: the next K block's barrier was seen complete
+    uint32_t scale_ready = 0;  // the next scale slot's barrier was seen complete
     uint32_t cphase = 0, sphase = 0;
     bool ok = true;
 
@@ -946,6 +947,7 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         // 32 columns at a time: a scale-row boundary can fall on any multiple of 32 columns
 #pragma unroll
         for (int q = 0; q < CC / 32; ++q) {
+
           const int cb = ch * CC + 32 * q;  // offset inside this thread's columns
           const float s = (((gcol0 + cb) >> 7) == jb0) ? slo : shi;
           if (cb < kPackedCols) {
@@ -963,10 +965,14 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         // Scales of the next (up to) four K blocks: three 16-byte shared-memory loads, then the
         // slot goes back to the loader.
         // (the vote makes the outcome the same in every lane: the warp-wide TMEM fetches below need all 32)
-        if (!warp_wait(smem_u32(&scale_full_bar[slot]), sphase, 0x600 | slot)) {
-          ok = false;
-          break;
+        // (the barrier was probed during the previous group's last fmas: scale_ready)
+        if (!__all_sync(0xffffffffu, scale_ready)) {
+          if (!warp_wait(smem_u32(&scale_full_bar[slot]), sphase, 0x600 | slot)) {
+            ok = false;
+            break;
+          }
         }
+        scale_ready = 0;
         const float4* sl = reinterpret_cast<const float4*>(scale_ring + slot * kScaleSlotFloats);
         constexpr int kQ = kScaleGroup / 4;  // float4s per row of a slot
         float s_lo[kScaleGroup], s_hi[kScaleGroup];
@@ -1030,6 +1036,11 @@ fp8_mm_blockscaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 }
                 ready_next = mbar_test(ready_base + static_cast<uint32_t>(ns * 8), np);
               }
+              // The next group's scales: a non-blocking probe of their slot's barrier, issued here so that its
+              // answer arrives under this K block's fmas. The loader runs slots ahead, so the answer is normally
+              // yes and the blocking wait (a few hundred clocks even on a complete barrier while the
+              // shared-memory path is busy) is skipped.
+              if (u == kScaleGroup - 1) scale_ready = mbar_test(smem_u32(&scale_full_bar[slot]), sphase);
             }
 #ifdef FP8MM_X_NOPROMO
             if (ch > 0) continue;
