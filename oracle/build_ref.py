@@ -18,8 +18,8 @@ variables the driver sets. Everything else - the `[k][m]` / `[k][n]` storage, th
 `k_idx / 128 * m + m_idx` and `k_idx / 128 * ((n + 127) / 128) + n_idx / 128` scale indexing,
 the fp32 multiply - is the reference's own code as compiled.
 
-The reference checkout is looked for in $FP8MM_REFERENCE_ROOT, else /root/reference. On a
-machine without it the recipe does nothing and the prebuilt library (if it travelled) is used."""
+The reference checkout is looked for in $FP8MM_REFERENCE_ROOT, else in the default location of
+`reference_root()`. On a machine without it the recipe does nothing and the prebuilt library (if it travelled) is used."""
 from __future__ import annotations
 
 import os
