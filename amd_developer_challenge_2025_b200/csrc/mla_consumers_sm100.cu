@@ -22,15 +22,21 @@ __device__ __forceinline__ __nv_bfloat16 bdiv(__nv_bfloat16 a, __nv_bfloat16 b) 
 
 // The rotation's (cos, sin) for position row i1 and pair index j: a function of (i1, j) only
 // (3-amd-mla-decode/amd-mla-submission.py:21-31).
-__device__ __forceinline__ void rope_angle(int pos, int i1, int j, int d2, __nv_bfloat16* c, __nv_bfloat16* s) {
-  const __nv_bfloat16 idx = badd(bf(static_cast<float>(pos)), bf(static_cast<float>(i1)));
+// The part that depends on the pair index alone: 10000^(-2j/d2), every step rounded to bf16.
+__device__ __forceinline__ __nv_bfloat16 rope_base(int j, int d2) {
   __nv_bfloat16 theta = bf(static_cast<float>(j));
   theta = bmul(theta, bf(-2.0f));
   theta = bdiv(theta, bf(static_cast<float>(d2)));
-  theta = bf(powf(fl(bf(10000.0f)), fl(theta)));
-  theta = bmul(theta, idx);
-  *c = bf(cosf(fl(theta)));
-  *s = bf(sinf(fl(theta)));
+  return bf(powf(fl(bf(10000.0f)), fl(theta)));
+}
+__device__ __forceinline__ void rope_rotation(__nv_bfloat16 base, int pos, int i1, __nv_bfloat16* c, __nv_bfloat16* s) {
+  const __nv_bfloat16 idx = badd(bf(static_cast<float>(pos)), bf(static_cast<float>(i1)));
+  const float theta = fl(bmul(base, idx));
+  *c = bf(cosf(theta));
+  *s = bf(sinf(theta));
+}
+__device__ __forceinline__ void rope_angle(int pos, int i1, int j, int d2, __nv_bfloat16* c, __nv_bfloat16* s) {
+  rope_rotation(rope_base(j, d2), pos, i1, c, s);
 }
 
 // One thread owns one (i1, j) pair and a share of the d0 rows: the angle is computed once and reused for
@@ -58,6 +64,8 @@ __global__ void __launch_bounds__(256) rope_kernel(const __nv_bfloat16* __restri
   }
 }
 
+constexpr int kRopeTable = 256;  // pair indices whose 10000^(-2j/d2) a CTA keeps in shared memory
+
 // The same with eight adjacent pair indices per thread: 16-byte loads and stores. Used when d2/2 is a multiple of 8
 // and every row start is 16-byte aligned (checked by the launcher).
 __global__ void __launch_bounds__(256) rope_kernel_vec8(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* y, int pos,
@@ -65,6 +73,14 @@ __global__ void __launch_bounds__(256) rope_kernel_vec8(const __nv_bfloat16* __r
                                                         long long ys1, long long ys2, int rows_per_block) {
   const int half = d2 >> 1;
   const int groups = half >> 3;  // groups of eight pair indices per position row
+  // 10000^(-2j/d2) depends on j alone: the CTA computes the table once (powf is about half of a thread's angle
+  // arithmetic) when it fits; every thread then needs only a cosf and a sinf per pair index.
+  __shared__ __nv_bfloat16 base_tab[kRopeTable];
+  const bool use_tab = half <= kRopeTable;
+  if (use_tab) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) base_tab[j] = rope_base(j, d2);
+    __syncthreads();
+  }
   const long long g = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (g >= static_cast<long long>(d1) * groups) return;
   const int i1 = static_cast<int>(g / groups);
@@ -73,7 +89,7 @@ __global__ void __launch_bounds__(256) rope_kernel_vec8(const __nv_bfloat16* __r
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     __nv_bfloat16 ce, se;
-    rope_angle(pos, i1, j0 + e, d2, &ce, &se);
+    rope_rotation(use_tab ? base_tab[j0 + e] : rope_base(j0 + e, d2), pos, i1, &ce, &se);
     c[e] = ce;
     s[e] = se;
   }
