@@ -1495,9 +1495,10 @@ struct WidthCost {
 
 WidthCost width_cost(int bn, int pair) {
   // CTA pairs: each CTA loads half of the B tile, which pays per K block at the wide tiles (192: 5 % fewer
-  // clocks than single CTAs, 256: 12 % fewer; K <= 512 loses 2-5 % to the dearer tile turnaround). At 64 and
-  // 128 columns pairs measured slower throughout. Plans with a split-K tail measured about 7 % above this
-  // model, hence the larger constant.
+  // clocks than single CTAs, 256: 12 % fewer; K <= 512 loses 2-5 % to the dearer tile turnaround). At 128
+  // columns pairs measured slower throughout; at 64 columns they are 3-6 % faster when no tile is split (2048 x
+  // 576, 2048 x 512 and 512 x 1536 with K = 7168: one wave of 72, 64 and 48 pair tiles) and about 10 % slower
+  // with split K. Plans with a split-K tail measured about 7 % above this model, hence the larger constant.
   if (pair && bn == 192) return {775.0, 3600.0, 12000.0, 1000.0};
   if (pair && bn == 256) return {930.0, 3600.0, 14000.0, 1500.0};
   switch (bn) {
@@ -1509,7 +1510,11 @@ WidthCost width_cost(int bn, int pair) {
 }
 
 // What a pair plan's cost is multiplied by, for the widths without a table of their own.
-double pair_penalty(int bn) { return bn >= 192 ? 1.0 : 1.04; }
+double pair_penalty(int bn, int split) {
+  if (bn >= 192) return 1.0;
+  if (bn == 64) return split > 1 ? 1.08 : 0.96;
+  return 1.04;
+}
 
 struct Candidate {
   int bn, pair, split, full_tiles;
@@ -1531,7 +1536,7 @@ Candidate evaluate(int M, int N, int kblocks, int sm_count, int bn, int pair, in
   };
   Candidate best{bn, pair, 1, tiles, ceil_div(tiles, units) * (kblocks * wc.per_kblock + wc.per_tile)};
   if (forced_split == 1 || kblocks < 8) {
-    if (pair) best.cost *= pair_penalty(bn);
+    if (pair) best.cost *= pair_penalty(bn, best.split);
     return best;
   }
   if (tiles * 2 <= units || (forced_split > 1 && tiles <= units)) {
@@ -1553,7 +1558,7 @@ Candidate evaluate(int M, int N, int kblocks, int sm_count, int bn, int pair, in
       if (cost < best.cost || forced_split > 1) best = Candidate{bn, pair, split, tiles - tail, cost};
     }
   }
-  if (pair) best.cost *= pair_penalty(bn);
+  if (pair) best.cost *= pair_penalty(bn, best.split);
   return best;
 }
 
